@@ -1,0 +1,149 @@
+"""The cache of a running engine: a slot per sequence, keys and values per cache entry, fixed-size state.
+
+Cache entries (one per schedule entry that owns a cache) are grouped by what they need: entries that keep the same
+number of key/value heads of the same size over the same span (all positions, or a window) share one group, and
+each group has storage of its own: a pool of pages ``[entry][page][k|v][kv head][position in page][head_dim]`` and
+a page table ``[slot][block]`` on the device. Entries that ask for a fixed-size state get a 32-bit tensor
+``[slot][...]`` that is zeroed when a slot is taken.
+
+Lengths are per sequence. A slot is taken when a sequence starts and given back when it ends; pages and slots that
+were given back are handed out again first. The reference's counterpart is one sequence's buffers
+(``kindi/nanbeige.py:587-594``) and, for its hybrid engine, recurrent state beside keys and values
+(``kindi/engine.py:228-232,306-308``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..parts.base import KVNeed, StateNeed
+from .pages import PAGE, CacheError, CacheFull, FreeList, PageMap, pages_for
+
+
+@dataclass
+class KVGroup:
+    need: KVNeed
+    entries: List[int]                 # cache entry indices, in pool order
+    pool: torch.Tensor                 # [len(entries), n_pages, 2, n_kv, PAGE, head_dim]
+    table: torch.Tensor                # int32 [n_slots, n_pages] on the device, -1 = not mapped
+    pages: PageMap
+
+
+class SequenceCache:
+    def __init__(self, needs: Sequence, *, max_tokens: int, n_slots: int, dtype: torch.dtype, device):
+        """``needs[i]`` is the KVNeed / StateNeed / None of cache entry i. ``max_tokens`` is the most tokens all
+        live sequences hold together, each sequence's count rounded up to a page."""
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.n_pages = max(1, pages_for(max_tokens))
+        self.n_slots = max(1, min(n_slots, self.n_pages))
+        self.slots = FreeList(self.n_slots, "sequence slot")
+        self.length: List[int] = [0] * self.n_slots
+        self.groups: List[KVGroup] = []
+        self._where: Dict[int, Tuple[int, int]] = {}          # cache entry -> (group index, index in group)
+        self.state: Dict[int, torch.Tensor] = {}
+        by_need: Dict[KVNeed, List[int]] = {}
+        for i, need in enumerate(needs):
+            if isinstance(need, KVNeed):
+                by_need.setdefault(need, []).append(i)
+            elif isinstance(need, StateNeed):
+                self.state[i] = torch.zeros((self.n_slots,) + tuple(need.shape), dtype=torch.float32,
+                                            device=self.device)
+            elif need is not None:
+                raise TypeError("cache entry %d asks for %r; a part's cache_need must be KVNeed, StateNeed or None"
+                                % (i, need))
+        for need, entries in by_need.items():
+            pool = torch.zeros((len(entries), self.n_pages, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype,
+                               device=self.device)
+            table = torch.full((self.n_slots, self.n_pages), -1, dtype=torch.int32, device=self.device)
+            g = KVGroup(need, entries, pool, table, PageMap(self.n_pages, self.n_slots, need.window))
+            for j, e in enumerate(entries):
+                self._where[e] = (len(self.groups), j)
+            self.groups.append(g)
+
+    # ------------------------------------------------------------------ sizes
+    @staticmethod
+    def bytes_needed(needs: Sequence, max_tokens: int, n_slots: int, dtype: torch.dtype) -> int:
+        n_pages = max(1, pages_for(max_tokens))
+        el = torch.empty((), dtype=dtype).element_size()
+        total = 0
+        seen = set()
+        for need in needs:
+            if isinstance(need, KVNeed):
+                total += n_pages * 2 * need.n_kv_heads * PAGE * need.head_dim * el
+                if need not in seen:
+                    seen.add(need)
+                    total += min(n_slots, n_pages) * n_pages * 4
+            elif isinstance(need, StateNeed):
+                total += min(n_slots, n_pages) * int(np.prod(need.shape)) * 4
+        return total
+
+    def kv_bytes_per_token(self) -> int:
+        el = torch.empty((), dtype=self.dtype).element_size()
+        return sum(len(g.entries) * 2 * g.need.n_kv_heads * g.need.head_dim * el for g in self.groups)
+
+    # ------------------------------------------------------------------ slots
+    def alloc_slot(self) -> int:
+        s = self.slots.take()
+        self.length[s] = 0
+        for t in self.state.values():
+            t[s].zero_()
+        return s
+
+    def free_slot(self, slot: int) -> None:
+        self.slots.give(slot)
+        for g in self.groups:
+            g.pages.release(slot)
+        self.length[slot] = 0
+
+    def reserve(self, slot: int, new_len: int) -> None:
+        """map pages so that positions below new_len can be written and read; raises CacheFull (nothing changed)"""
+        if not self.slots.held(slot):
+            raise CacheError("slot %d is not in use" % slot)
+        done: List[KVGroup] = []
+        for g in self.groups:
+            g.pages.ensure(slot, new_len)
+            done.append(g)
+
+    def commit(self, slot: int, new_len: int) -> None:
+        """the step that stored positions up to new_len has been issued"""
+        self.length[slot] = new_len
+        for g in self.groups:
+            g.pages.trim(slot, new_len)
+
+    def flush(self) -> None:
+        """bring the device page tables up to date (before a step's kernels are launched)"""
+        for g in self.groups:
+            dirty = g.pages.take_dirty()
+            if not dirty:
+                continue
+            last: Dict[Tuple[int, int], int] = {}
+            for s, b, pg in dirty:
+                last[(s, b)] = pg
+            idx = torch.tensor([s * self.n_pages + b for (s, b) in last], dtype=torch.int64)
+            val = torch.tensor(list(last.values()), dtype=torch.int32)
+            g.table.view(-1).index_copy_(0, idx.to(self.device), val.to(self.device))
+
+    # ------------------------------------------------------------------ views for the parts
+    def kv_view(self, entry: int):
+        """(pool of this entry [n_pages, 2, n_kv, PAGE, head_dim], page table, number of pages)"""
+        gi, j = self._where[entry]
+        g = self.groups[gi]
+        return g.pool[j], g.table, self.n_pages
+
+    def state_view(self, entry: int) -> torch.Tensor:
+        return self.state[entry]
+
+    def tokens_held(self) -> int:
+        return max((g.pages.pool.n_held for g in self.groups), default=0) * PAGE
+
+    def check(self) -> None:
+        self.slots.check()
+        for g in self.groups:
+            g.pages.check()
+            for s in range(self.n_slots):
+                if not self.slots.held(s) and g.pages.rows[s]:
+                    raise CacheError("free slot %d still maps %d pages" % (s, len(g.pages.rows[s])))

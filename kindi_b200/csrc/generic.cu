@@ -1,0 +1,337 @@
+// Plain kernels for every operation of a step, templated on the storage type.
+//
+// With float storage they ARE the true 32-bit path of the model: no tensor cores, no reduced-precision matrix
+// mode, no fast-math intrinsics; every sum is taken in an order that depends only on absolute positions and on the
+// operand's own indices, never on how many rows share the launch, so logits do not change with the way the work is
+// cut. With bfloat16 storage they are the slow-but-general versions of the serving kernels (every head size in
+// steps of 2, any number of heads and groups), kept as the reference beside each fast kernel.
+//
+// Formulas follow the reference's order of operations: fused residual add + RMS norm (kindi/nbq.cu:412-453),
+// rotary position encoding with individually rounded products (kindi/nbq.cu:127-130; rotate-half pairing as
+// kindi/dspine.cu:151-174), attention with an online softmax over runs of 32 positions and a running maximum that
+// starts at -1e30 (kindi/nbq.cu:525-633), SwiGLU g / (1 + exp(-g)) * u (kindi/nbq.cu:461-467).
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------------ embedding
+// x[t][:] = table[tok[t]][:] as 32-bit (no scaling: kindi/nbq.cu:472-487)
+template <typename TW>
+__global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ tok, float* __restrict__ x, int E,
+                        int vocab, int* status) {
+    const int t = blockIdx.x;
+    const int id = tok[t];
+    float* xr = x + (size_t)t * E;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, KB_ST_BAD_TOKEN);
+        for (int i = threadIdx.x; i < E; i += blockDim.x) xr[i] = 0.0f;
+        return;
+    }
+    const TW* row = table + (size_t)id * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) xr[i] = kb_to_f<TW>(row[i]);
+}
+
+extern "C" int kb_embed(const void* table, int wdtype, const int* tok, float* x, int T, int E, int vocab,
+                        int* status, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (wdtype == KB_F32) k_embed<float><<<T, 256, 0, st>>>((const float*)table, tok, x, E, vocab, status);
+    else k_embed<bf16><<<T, 256, 0, st>>>((const bf16*)table, tok, x, E, vocab, status);
+    KB_LAUNCH_RET();
+}
+
+// ------------------------------------------------------------------------------------------------ add + RMS norm
+// row r of the output is row t = rows ? rows[r] : r of the residual. v = x[t] + sum_s delta[s][t] (s in order);
+// written back to x when write_back; y = (rsqrt(mean(v^2) + eps) * v) * w, the two products rounded one after the
+// other as the reference does (kindi/nbq.cu:428-430).
+template <typename TY, typename TW>
+__global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ x, const float* __restrict__ delta,
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, TY* __restrict__ y,
+        const int* __restrict__ rows, int T, int E, int write_back, int* status) {
+    extern __shared__ float sv[];
+    __shared__ float red[8];
+    const int r = blockIdx.x;
+    int t = rows ? rows[r] : r;
+    if (t < 0 || t >= T) {
+        if (threadIdx.x == 0) atomicOr(status, KB_ST_BAD_ROW);
+        t = 0;
+    }
+    float* xr = x + (size_t)t * E;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < E; i += 256) {
+        float v = xr[i];
+        for (int s = 0; s < n_delta; s++) v += delta[(size_t)s * delta_stride + (size_t)t * E + i];
+        if (write_back) xr[i] = v;
+        sv[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = kb_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = red[0];
+#pragma unroll
+    for (int k = 1; k < 8; k++) tot += red[k];
+    const float scale = rsqrtf(tot / (float)E + eps);
+    TY* yr = y + (size_t)r * E;
+    for (int i = threadIdx.x; i < E; i += 256)
+        yr[i] = kb_from_f<TY>(__fmul_rn(__fmul_rn(scale, sv[i]), kb_to_f<TW>(w[i])));
+}
+
+extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long long delta_stride, const void* w,
+                              int wdtype, float eps, void* y, int ydtype, const int* rows, int n_out, int T, int E,
+                              int write_back, int* status, cudaStream_t st) {
+    if (n_out <= 0) return 0;
+    size_t sm = (size_t)E * sizeof(float);
+    if (sm > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define KB_NORM(TY, TW)                                                                                       \
+    do {                                                                                                      \
+        if (sm > 48 * 1024)                                                                                   \
+            cudaFuncSetAttribute(k_add_rmsnorm<TY, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+        k_add_rmsnorm<TY, TW><<<n_out, 256, sm, st>>>(x, delta, n_delta, (size_t)delta_stride, (const TW*)w,  \
+                                                      eps, (TY*)y, rows, T, E, write_back, status);           \
+    } while (0)
+    if (ydtype == KB_F32 && wdtype == KB_F32) KB_NORM(float, float);
+    else if (ydtype == KB_F32) KB_NORM(float, bf16);
+    else if (wdtype == KB_F32) KB_NORM(bf16, float);
+    else KB_NORM(bf16, bf16);
+#undef KB_NORM
+    KB_LAUNCH_RET();
+}
+
+// ------------------------------------------------------------------------------------------------ matrix product
+// C[m][n] = sum_k A[m][k] * W[n][k]; each output's sum runs over k = 0, 1, 2, ... in order with 32-bit fused
+// multiply-adds, so an output does not depend on the tile it lands in or on how many rows there are.
+#define GS_BM 64
+#define GS_BN 64
+#define GS_BK 16
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) k_gemm_simt(const TA* __restrict__ A, const TW* __restrict__ W,
+        TC* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
+    __shared__ float As[GS_BK][GS_BM + 1];
+    __shared__ float Ws[GS_BK][GS_BN + 1];
+    const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += GS_BK) {
+        for (int e = tid; e < GS_BM * GS_BK; e += 256) {
+            int r = e / GS_BK, c = e % GS_BK;
+            int m = m0 + r, k = k0 + c;
+            As[c][r] = (m < M && k < K) ? kb_to_f<TA>(A[(size_t)m * lda + k]) : 0.0f;
+            int n = n0 + r;
+            Ws[c][r] = (n < N && k < K) ? kb_to_f<TW>(W[(size_t)n * ldw + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GS_BK; k++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int n = n0 + tx * 4 + j;
+            if (n < N) C[(size_t)m * ldc + n] = kb_from_f<TC>(acc[i][j]);
+        }
+    }
+}
+
+extern "C" int kb_gemm_simt(const void* A, int adtype, const void* W, int wdtype, void* C, int cdtype, int M, int N,
+                            int K, int lda, int ldw, int ldc, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
+#define KB_G(TA, TW, TC) \
+    k_gemm_simt<TA, TW, TC><<<grid, 256, 0, st>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc)
+    int code = adtype * 4 + wdtype * 2 + cdtype;
+    switch (code) {
+        case 0: KB_G(float, float, float); break;
+        case 1: KB_G(float, float, bf16); break;
+        case 2: KB_G(float, bf16, float); break;
+        case 3: KB_G(float, bf16, bf16); break;
+        case 4: KB_G(bf16, float, float); break;
+        case 5: KB_G(bf16, float, bf16); break;
+        case 6: KB_G(bf16, bf16, float); break;
+        default: KB_G(bf16, bf16, bf16); break;
+    }
+#undef KB_G
+    KB_LAUNCH_RET();
+}
+
+// ------------------------------------------------------------------------------------------------ rotary + store
+// qkv: [T][(nh + 2 nkv) * hd] (q heads, then k heads, then v heads). Query heads are rotated in place; key heads
+// are rotated and written to the cache at (slot of the row's sequence, the row's position); value heads are
+// copied there. The rotation pairs element i with i + rot/2 (i < rot/2; elements from rot on pass through); the
+// angle is (float)pos * inv_freq[i] in 32-bit, cosine and sine by the accurate library functions, and the four
+// products are rounded one by one (kindi/nbq.cu:127-130).
+template <typename T>
+__global__ void k_rope_store(T* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rot,
+        const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
+        int hd, KbCacheView cv, int* status) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int p = pos[t];
+    T* src = qkv + (size_t)t * ld + (size_t)h * hd;
+    T* dst = src;
+    const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+    if (!is_q) {
+        const int hk = is_k ? h - nh : h - nh - nkv;
+        const int s = slot[seq[t]];
+        const int page = cv.table[(size_t)s * cv.table_stride + p / KB_PAGE];
+        if (page < 0 || page >= cv.n_pages) {
+            if (threadIdx.x == 0) atomicOr(status, KB_ST_BAD_PAGE);
+            return;
+        }
+        dst = (T*)cv.pool + kb_kv_offset(cv, page, is_k ? 0 : 1, hk, p % KB_PAGE);
+    }
+    const int half = rot / 2;
+    if (is_q || is_k) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float ang = __fmul_rn((float)p, inv_freq[i]);
+            const float c = cosf(ang), s = sinf(ang);
+            const float a = kb_to_f<T>(src[i]), b = kb_to_f<T>(src[i + half]);
+            dst[i] = kb_from_f<T>(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
+            dst[i + half] = kb_from_f<T>(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
+        }
+        if (dst != src)
+            for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+    } else {
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+extern "C" int kb_rope_store(void* qkv, int dtype, int ld, const float* inv_freq, int rot, const int* pos,
+                             const int* seq, const int* slot, int T, int nh, int nkv, int hd, void* pool,
+                             const int* table, int table_stride, int n_pages, int* status, cudaStream_t st) {
+    if (T <= 0) return 0;
+    KbCacheView cv{pool, table, table_stride, n_pages, nkv, hd};
+    dim3 grid(T, nh + 2 * nkv);
+    int thr = hd / 2 < 32 ? 32 : (hd / 2 > 128 ? 128 : ((hd / 2 + 31) / 32) * 32);
+    if (dtype == KB_F32)
+        k_rope_store<float><<<grid, thr, 0, st>>>((float*)qkv, ld, inv_freq, rot, pos, seq, slot, nh, nkv, hd, cv, status);
+    else
+        k_rope_store<bf16><<<grid, thr, 0, st>>>((bf16*)qkv, ld, inv_freq, rot, pos, seq, slot, nh, nkv, hd, cv, status);
+    KB_LAUNCH_RET();
+}
+
+// ------------------------------------------------------------------------------------------------ attention
+// One warp per (row, query head). The row attends the keys of its sequence at positions lo..pos, lo = 0 or
+// pos - window + 1, read from the cache. Keys are taken in runs of 32 that start at multiples of 32 of the absolute
+// position (lane = position for the scores, lane = dimension for P V) with a running maximum and sum, so the order
+// of every sum depends on positions only: the same row gives the same bits whether it came in a prompt or alone.
+#define AG_MAX_HD 256
+template <typename T>
+__global__ void __launch_bounds__(128) k_attn_generic(const T* __restrict__ q, int ldq, T* __restrict__ out,
+        int ldo, const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int Tn,
+        int nh, int group, int hd, float scale, int window, KbCacheView cv, int* status) {
+    __shared__ float qs[4][AG_MAX_HD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)Tn * nh) return;
+    const int t = (int)(item / nh), h = (int)(item % nh);
+    const int hk = h / group;
+    const int p_q = pos[t];
+    const int s = slot[seq[t]];
+    const T* qr = q + (size_t)t * ldq + (size_t)h * hd;
+    for (int d = lane; d < hd; d += 32) qs[warp][d] = __fmul_rn(kb_to_f<T>(qr[d]), scale);
+    __syncwarp();
+    const int lo = (window > 0 && p_q - window + 1 > 0) ? p_q - window + 1 : 0;
+    const int* trow = cv.table + (size_t)s * cv.table_stride;
+    float m = -1e30f, l = 0.0f;
+    float o[AG_MAX_HD / 32];
+#pragma unroll
+    for (int i = 0; i < AG_MAX_HD / 32; i++) o[i] = 0.0f;
+    for (int c0 = lo & ~31; c0 <= p_q; c0 += 32) {
+        const int p = c0 + lane;
+        const bool live = p >= lo && p <= p_q;
+        float sc = -1e30f;
+        const T* vrow = nullptr;
+        bool ok = live;
+        if (live) {
+            const int page = trow[p / KB_PAGE];
+            if (page < 0 || page >= cv.n_pages) {
+                atomicOr(status, KB_ST_BAD_PAGE);
+                ok = false;
+            } else {
+                const T* kr = (const T*)cv.pool + kb_kv_offset(cv, page, 0, hk, p % KB_PAGE);
+                vrow = (const T*)cv.pool + kb_kv_offset(cv, page, 1, hk, p % KB_PAGE);
+                float a = 0.0f;
+                for (int d = 0; d < hd; d++) a = fmaf(qs[warp][d], kb_to_f<T>(kr[d]), a);
+                sc = a;
+            }
+        }
+        const float mx = kb_warp_max(ok ? sc : -1e30f);
+        const float mn = fmaxf(m, mx);
+        const float f = expf(m - mn);
+        const float pr = ok ? expf(sc - mn) : 0.0f;
+        l = l * f + kb_warp_sum(pr);
+        m = mn;
+#pragma unroll
+        for (int i = 0; i < AG_MAX_HD / 32; i++) o[i] *= f;
+        const unsigned mask = __ballot_sync(0xffffffffu, ok);
+        for (int j = 0; j < 32; j++) {
+            if (!((mask >> j) & 1u)) continue;
+            const float pj = __shfl_sync(0xffffffffu, pr, j);
+            const T* vj = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)vrow, j);
+#pragma unroll
+            for (int i = 0; i < AG_MAX_HD / 32; i++) {
+                const int d = i * 32 + lane;
+                if (d < hd) o[i] = fmaf(pj, kb_to_f<T>(vj[d]), o[i]);
+            }
+        }
+    }
+    T* orow = out + (size_t)t * ldo + (size_t)h * hd;
+#pragma unroll
+    for (int i = 0; i < AG_MAX_HD / 32; i++) {
+        const int d = i * 32 + lane;
+        if (d < hd) orow[d] = kb_from_f<T>(o[i] / l);
+    }
+}
+
+extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int ldo, const int* pos, const int* seq,
+                               const int* slot, int T, int nh, int nkv, int hd, float scale, int window, void* pool,
+                               const int* table, int table_stride, int n_pages, int* status, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (hd > AG_MAX_HD || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+    KbCacheView cv{pool, table, table_stride, n_pages, nkv, hd};
+    long long items = (long long)T * nh;
+    int grid = (int)((items + 3) / 4);
+    if (dtype == KB_F32)
+        k_attn_generic<float><<<grid, 128, 0, st>>>((const float*)q, ldq, (float*)out, ldo, pos, seq, slot, T, nh,
+                                                   nh / nkv, hd, scale, window, cv, status);
+    else
+        k_attn_generic<bf16><<<grid, 128, 0, st>>>((const bf16*)q, ldq, (bf16*)out, ldo, pos, seq, slot, T, nh,
+                                                  nh / nkv, hd, scale, window, cv, status);
+    KB_LAUNCH_RET();
+}
+
+// ------------------------------------------------------------------------------------------------ SwiGLU
+// gu: [T][2F] = gate then up; out[t][i] = gate / (1 + exp(-gate)) * up (kindi/nbq.cu:461-467)
+template <typename T>
+__global__ void k_swiglu(const T* __restrict__ gu, T* __restrict__ out, int F, long long total) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / F;
+    const int c = (int)(i % F);
+    const float g = kb_to_f<T>(gu[t * 2 * F + c]), u = kb_to_f<T>(gu[t * 2 * F + F + c]);
+    out[i] = kb_from_f<T>(g / (1.0f + expf(-g)) * u);
+}
+
+extern "C" int kb_swiglu(const void* gu, void* out, int dtype, int T, int F, cudaStream_t st) {
+    long long total = (long long)T * F;
+    if (total <= 0) return 0;
+    int grid = (int)((total + 255) / 256);
+    if (dtype == KB_F32) k_swiglu<float><<<grid, 256, 0, st>>>((const float*)gu, (float*)out, F, total);
+    else k_swiglu<bf16><<<grid, 256, 0, st>>>((const bf16*)gu, (bf16*)out, F, total);
+    KB_LAUNCH_RET();
+}

@@ -1,0 +1,94 @@
+"""Packing the sequences of one step: the host-side arithmetic that turns "these sequences bring these tokens" into
+the arrays the kernels read. Pure Python + NumPy, so it is testable without a GPU.
+
+Rows are the new tokens of all sequences, one sequence after another (unequal lengths, no padding). For row r of
+sequence b: ``pos = length_before[b] + offset``, ``seq = b``. ``want`` places are offsets into a sequence's own
+tokens; ``rows`` are the packed row numbers, in the order of the entries and of their ``want`` lists.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence, Tuple
+
+import numpy as np
+
+
+@dataclass(frozen=True)
+class StepEntry:
+    """one sequence's share of a step: its slot, its next tokens, and the places among them whose logits are
+    wanted"""
+
+    slot: int
+    tokens: Tuple[int, ...]
+    want: Tuple[int, ...] = ()
+
+
+@dataclass
+class PackedStep:
+    T: int
+    B: int
+    R: int
+    meta: np.ndarray                  # int32, all segments one after another
+    off: dict                         # segment name -> (start, length)
+    h_slot: Tuple[int, ...]
+    h_q_start: Tuple[int, ...]
+    h_kv_len: Tuple[int, ...]
+    decode: bool
+    max_q: int
+    max_kv: int
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+def layout(T: int, B: int, R: int) -> Tuple[dict, int]:
+    """where each segment lies in the meta buffer; depends on the three counts only, so steps of the same shape
+    share it"""
+    off, at = {}, 0
+    for name, n in (("tok", T), ("pos", T), ("seq", T), ("slot", B), ("q_start", B + 1), ("kv_len", B),
+                    ("rows", R)):
+        off[name] = (at, n)
+        at += _align(max(n, 1))
+    return off, at
+
+
+def pack(entries: Sequence[StepEntry], length_before: Sequence[int]) -> PackedStep:
+    if not entries:
+        raise ValueError("a step needs at least one sequence")
+    slots = [e.slot for e in entries]
+    if len(set(slots)) != len(slots):
+        raise ValueError("a slot appears twice in one step: %r" % (slots,))
+    q_len = [len(e.tokens) for e in entries]
+    if min(q_len) < 1:
+        raise ValueError("every sequence of a step brings at least one token")
+    B, T = len(entries), sum(q_len)
+    rows: List[int] = []
+    q_start = [0]
+    for e, n in zip(entries, q_len):
+        for w in e.want:
+            if not (0 <= w < n):
+                raise ValueError("want place %d lies outside the sequence's %d tokens of this step" % (w, n))
+            rows.append(q_start[-1] + w)
+        q_start.append(q_start[-1] + n)
+    R = len(rows)
+    off, total = layout(T, B, R)
+    meta = np.zeros(total, dtype=np.int32)
+
+    def seg(name):
+        a, n = off[name]
+        return meta[a:a + n]
+    tok, pos, seq = seg("tok"), seg("pos"), seg("seq")
+    kv_len = []
+    for b, (e, n) in enumerate(zip(entries, q_len)):
+        a = q_start[b]
+        tok[a:a + n] = e.tokens
+        pos[a:a + n] = np.arange(length_before[b], length_before[b] + n, dtype=np.int32)
+        seq[a:a + n] = b
+        kv_len.append(length_before[b] + n)
+    seg("slot")[:] = slots
+    seg("q_start")[:] = q_start
+    seg("kv_len")[:] = kv_len
+    seg("rows")[:] = rows
+    return PackedStep(T=T, B=B, R=R, meta=meta, off=off, h_slot=tuple(slots), h_q_start=tuple(q_start),
+                      h_kv_len=tuple(kv_len), decode=max(q_len) == 1, max_q=max(q_len), max_kv=max(kv_len))

@@ -1,0 +1,166 @@
+"""The engine: a model, its cache and ONE step function.
+
+``step`` takes a batch of sequences, each with its next tokens (a whole prompt, or one token, or any run in
+between) and the places whose logits are wanted. It runs only those tokens, as one packed batch, against the cache
+that earlier steps left, stores their keys and values, and returns 32-bit logits at the wanted places. There is
+no padding, so no result can depend on it; a row's logits do not depend on what else is in the batch.
+
+The reference has three entry points for one sequence - ``step`` (one token, ``kindi/nanbeige.py:736-776``),
+``prefill_batch`` (a prompt in chunks, head on the last row, ``:962-1021``) and ``check`` (up to 8 rows with logits
+for each, ``:1144-1192``); this one function covers all three for a batch.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.pages import CacheFull
+from ..cache.sequence_cache import SequenceCache
+from ..config.model_config import ModelConfig
+from ..config.registry import architecture
+from ..config.spec import ModelSpec
+from ..kernels import lib as K
+from ..parts.base import StepContext
+from ..parts.model import DecoderModel, cache_needs, expected_tensors
+from ..weights.loader import load_tensors
+from .batch import PackedStep, StepEntry, pack
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+class Engine:
+    def __init__(self, model_dir: Optional[str] = None, *, ctx: int = 24576, dtype: str = "bfloat16",
+                 max_batch: int = 64, device: str = "cuda:0", spec: Optional[ModelSpec] = None,
+                 tensors: Optional[Mapping[str, torch.Tensor]] = None, log=None):
+        """``model_dir``: a folder with config.json and safetensors files; or give ``spec`` and ``tensors``
+        directly. ``ctx``: the most tokens all live sequences hold together (rounded up per sequence to the cache
+        page); it sizes the cache, like the reference's ``ctx`` (``kindi/nanbeige.py:245``)."""
+        if dtype not in _DTYPES:
+            raise EngineError("dtype must be 'bfloat16' or 'float32', not %r" % (dtype,))
+        if not torch.cuda.is_available():
+            raise EngineError("kindi_b200 runs on a CUDA GPU only (sm_100a); none is visible")
+        self.log = log or (lambda msg: None)
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        K.load()                                   # build / load the kernels now: fail loudly, not at first step
+        self.dtype_name = dtype
+        self.dtype = _DTYPES[dtype]
+        self.config: Optional[ModelConfig] = None
+        if spec is None:
+            if model_dir is None:
+                raise EngineError("give a model folder, or a spec with tensors")
+            self.config = ModelConfig.from_dir(model_dir)
+            spec = architecture(self.config.architecture).build_spec(self.config)
+        self.spec = spec
+        if tensors is None:
+            optional = ()
+            tensors = load_tensors(model_dir, expected_tensors(spec), run_dtype=dtype, device=str(self.device))
+        else:
+            tensors = {n: _to_run_dtype(t, dtype).to(self.device) for n, t in tensors.items()}
+        self.model = DecoderModel(spec, tensors, dtype=self.dtype, device=self.device)
+        self.ctx = int(ctx)
+        self.max_batch = int(max_batch)
+        self.cache = SequenceCache(cache_needs(spec), max_tokens=self.ctx, n_slots=self.max_batch,
+                                   dtype=self.dtype, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._pinned: Dict[int, torch.Tensor] = {}
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ slots
+    def alloc(self) -> int:
+        """take a slot for a sequence that starts"""
+        return self.cache.alloc_slot()
+
+    def free(self, slot: int) -> None:
+        """give back a sequence's slot and everything it holds"""
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length[slot]
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """run the entries' tokens as one batch; returns float32 logits ``[number of wanted places, vocab]`` on the
+        device (None when nothing is wanted). The cache then holds the tokens' keys and values."""
+        cache = self.cache
+        before = [cache.length[e.slot] for e in entries]
+        ps = pack(entries, before)
+        limit = self.spec.max_positions
+        reserved = []
+        try:
+            for e, new_len in zip(entries, ps.h_kv_len):
+                cache.reserve(e.slot, new_len)
+                reserved.append(e.slot)
+        except CacheFull as ex:
+            raise CacheFull("%s while storing %d new tokens; the cache holds %d tokens (ctx = %d)"
+                            % (ex, ps.T, cache.tokens_held(), self.ctx)) from None
+        ctx = self._context(ps)
+        cache.flush()
+        rows = ctx_rows = None
+        if ps.R:
+            a, n = ps.off["rows"]
+            rows = self._meta_dev[a:a + n]
+        logits = self.model.forward(ctx, rows)
+        for e, new_len in zip(entries, ps.h_kv_len):
+            cache.commit(e.slot, new_len)
+        self.steps_run += 1
+        return logits
+
+    def _context(self, ps: PackedStep) -> StepContext:
+        n = ps.meta.size
+        cap = 1 << max(6, (n - 1).bit_length())
+        pin = self._pinned.get(cap)
+        if pin is None:
+            pin = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._pinned[cap] = pin
+        # the previous step's copy from this buffer has finished: every step ends in a host read of its results or
+        # is followed by another step's copy on the same stream only after this write (copies are stream-ordered
+        # and the host waits below before reusing the buffer)
+        ev = getattr(self, "_copy_done", None)
+        if ev is not None:
+            ev.synchronize()
+        pin[:n] = torch.from_numpy(ps.meta)
+        dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        dev.copy_(pin[:n], non_blocking=True)
+        self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+        self._meta_dev = dev
+
+        def seg(name):
+            a, m = ps.off[name]
+            return dev[a:a + m]
+        return StepContext(T=ps.T, B=ps.B, tok=seg("tok"), pos=seg("pos"), seq=seg("seq"), slot=seg("slot"),
+                           q_start=seg("q_start"), kv_len=seg("kv_len"), h_slot=ps.h_slot,
+                           h_q_start=ps.h_q_start, h_kv_len=ps.h_kv_len, decode=ps.decode, max_q=ps.max_q,
+                           max_kv=ps.max_kv, dtype=self.dtype, device=self.device, status=self.status,
+                           cache=self.cache, fast=self.dtype == torch.bfloat16)
+
+    def check_status(self) -> None:
+        """raise if a kernel of an earlier step met an index it had to skip (waits for the device)"""
+        st = int(self.status.item())
+        if st:
+            self.status.zero_()
+            what = [n for bit, n in ((K.ST_BAD_TOKEN, "a token id outside the vocabulary"),
+                                     (K.ST_BAD_PAGE, "a cache position without a mapped page"),
+                                     (K.ST_WAIT_TIMEOUT, "a wait inside a kernel ran out"),
+                                     (K.ST_BAD_ROW, "a wanted row outside the step")) if st & bit]
+            raise EngineError("a kernel reported: %s (status %d); the step's results are not valid"
+                              % ("; ".join(what) or "unknown", st))
+
+    # ------------------------------------------------------------------ accounting
+    def weight_bytes_per_step(self, n_rows: int) -> int:
+        return self.model.bytes_read(n_rows)
+
+    def kv_bytes_per_token(self) -> int:
+        return self.cache.kv_bytes_per_token()
+
+
+def _to_run_dtype(t: torch.Tensor, run_dtype: str) -> torch.Tensor:
+    from ..weights.loader import target_dtype
+    return t.to(target_dtype(t.dtype, run_dtype))

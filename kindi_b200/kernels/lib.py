@@ -1,0 +1,176 @@
+"""Loading the kernel library and calling its entry points with torch tensors.
+
+The library is plain C ABI (``extern "C"``): raw device pointers, sizes and a stream. It is loaded with ctypes from
+the in-tree build folder; a missing or unbuildable library is an error, never a fallback to other code. Each
+wrapper below checks what the kernel itself does not (contiguity, dtypes, size limits) and raises on a failed
+launch.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_float, c_void_p, c_longlong
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+PAGE = 64                     # positions per cache page (KB_PAGE in csrc/common.cuh)
+
+ST_BAD_TOKEN, ST_BAD_PAGE, ST_WAIT_TIMEOUT, ST_BAD_ROW = 1, 2, 4, 8
+
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGS = {
+    "kb_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "kb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p,
+                       c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "kb_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                     c_void_p],
+    "kb_rope_store": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                      c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "kb_attn_generic": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "kb_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+}
+
+
+def load(verbose: bool = True):
+    """build (when needed) and load the kernel library; raises when that is not possible"""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.library_path(build=True, verbose=verbose)
+    lib = ctypes.CDLL(path)
+    for name, args in _SIGS.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            raise KernelError("kindi_b200: the kernel library %s lacks %s" % (path, name))
+        fn.argtypes = args
+        fn.restype = c_int
+    lib._path = path
+    _lib = lib
+    return lib
+
+
+def library_file() -> str:
+    return load()._path
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError("kindi_b200: launching %s failed with CUDA error %d (%s)"
+                          % (what, rc, _err_name(rc)))
+
+
+def _err_name(rc: int) -> str:
+    try:
+        return torch.cuda.cudart().cudaGetErrorString(rc)      # type: ignore[attr-defined]
+    except Exception:                                          # noqa: BLE001
+        return "?"
+
+
+def dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError("kindi_b200: tensors must be float32 or bfloat16, found %s" % t.dtype)
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kindi_b200: the kernels run on the GPU only; a tensor lives on %s" % t.device)
+
+
+# ----------------------------------------------------------------------------------------------- wrappers
+def embed(table: torch.Tensor, tok: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t] (float32 [T, E]) = table[tok[t]]"""
+    _need_cuda(table, tok, out)
+    T, E = out.shape
+    assert table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32 and tok.dtype == torch.int32
+    _check(load().kb_embed(_p(table), dt(table), _p(tok), _p(out), T, E, table.shape[0], _p(status), _stream()),
+           "embed")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor], write_back: bool, status: torch.Tensor) -> None:
+    """x (float32 [T, E]) + sum of delta ([S, T, E] float32) -> RMS norm * w -> out ([R, E]); rows int32 or None"""
+    _need_cuda(x, delta, w, out, rows)
+    T, E = x.shape
+    n_out = out.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and w.shape == (E,)
+    nd, stride = 0, 0
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and delta.shape[1:] == (T, E)
+        nd, stride = delta.shape[0], T * E
+    if rows is None:
+        assert n_out == T
+    else:
+        assert rows.dtype == torch.int32 and rows.numel() == n_out
+    if E * 4 > 200 * 1024:
+        raise KernelError("kindi_b200: RMS norm supports a width up to 51200, found %d" % E)
+    _check(load().kb_add_rmsnorm(_p(x), _p(delta), nd, stride, _p(w), dt(w), float(eps), _p(out), dt(out), _p(rows),
+                                 n_out, T, E, 1 if write_back else 0, _p(status), _stream()), "add_rmsnorm")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T with 32-bit accumulation in a fixed order (no tensor cores)"""
+    _need_cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(load().kb_gemm_simt(_p(a), dt(a), _p(w), dt(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0),
+                               out.stride(0), _stream()), "gemm_simt")
+
+
+def rope_store(qkv: torch.Tensor, inv_freq: torch.Tensor, rot: int, pos, seq, slot, nh: int, nkv: int, hd: int,
+               pool: Optional[torch.Tensor], table: torch.Tensor, n_pages: int, status: torch.Tensor) -> None:
+    """rotate the query heads of qkv ([T, (nh + 2 nkv) hd]) in place, rotate and store keys, store values"""
+    _need_cuda(qkv, inv_freq, pool, table)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot // 2
+    assert rot % 2 == 0 and rot <= hd
+    if pool is not None:
+        assert pool.dtype == qkv.dtype and pool.is_contiguous()
+    _check(load().kb_rope_store(_p(qkv), dt(qkv), qkv.stride(0), _p(inv_freq), rot, _p(pos), _p(seq), _p(slot), T,
+                                nh, nkv, hd, _p(pool), _p(table), table.stride(0), n_pages, _p(status), _stream()),
+           "rope_store")
+
+
+def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nkv: int, hd: int, scale: float,
+                 window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, status: torch.Tensor) -> None:
+    """attention of each row of q ([T, >= nh hd], row stride free) over its sequence's cached keys and values"""
+    _need_cuda(q, out, pool, table)
+    T = q.shape[0]
+    if hd > 256:
+        raise KernelError("kindi_b200: attention supports head sizes up to 256, found %d" % hd)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == pool.dtype
+    _check(load().kb_attn_generic(_p(q), dt(q), q.stride(0), _p(out), out.stride(0), _p(pos), _p(seq), _p(slot), T,
+                                  nh, nkv, hd, float(scale), int(window), _p(pool), _p(table), table.stride(0),
+                                  n_pages, _p(status), _stream()), "attn_generic")
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
+    """out[T, F] = silu(gu[:, :F]) * gu[:, F:]"""
+    _need_cuda(gu, out)
+    T, F = out.shape
+    assert gu.shape == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype
+    _check(load().kb_swiglu(_p(gu), _p(out), dt(gu), T, F, _stream()), "swiglu")

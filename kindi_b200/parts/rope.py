@@ -1,0 +1,37 @@
+"""Position encodings. The attention mixer asks its position encoding for the rotation table it hands to the
+fused rotate-and-store kernel: ``inv_freq[i]`` for each rotated pair and the number of rotated dimensions.
+
+Rotary (rotate-half pairing, for tensors in the safetensors layout): pair ``(i, i + rot/2)``, angle
+``float(pos) * inv_freq[i]`` with ``inv_freq[i] = base ** (-2 i / rot)`` rounded to 32-bit; the reference's form
+for such tensors is ``kindi/dspine.cu:151-174`` (angle in 32-bit, ``a c - b s`` / ``b c + a s``), its GGUF path
+rotates adjacent pairs of permuted rows, which is the same function (``kindi/nbq.cu:497-520``); the base defaults
+to 10000.0 (``kindi/nanbeige.py:256``). ``NoPosition`` rotates nothing.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.registry import register_part
+from .base import PositionEncoding
+
+
+class Rotary(PositionEncoding):
+    def __init__(self, spec, width, weights, *, dtype, device):
+        super().__init__(spec, width, weights, dtype=dtype, device=device)
+        self.base = float(spec["base"])
+        self.rotary_dim = int(spec["rotary_dim"])
+        if self.rotary_dim % 2 or self.rotary_dim <= 0:
+            raise ValueError("rotary_dim must be even and positive, found %d" % self.rotary_dim)
+        i = torch.arange(0, self.rotary_dim // 2, dtype=torch.float64)
+        self.inv_freq = (self.base ** (-2.0 * i / self.rotary_dim)).to(torch.float32).to(device)
+
+
+class NoPosition(PositionEncoding):
+    def __init__(self, spec, width, weights, *, dtype, device):
+        super().__init__(spec, width, weights, dtype=dtype, device=device)
+        self.rotary_dim = 0
+        self.inv_freq = torch.zeros(1, dtype=torch.float32, device=device)
+
+
+register_part("position", "rotary", Rotary)
+register_part("position", "none", NoPosition)
