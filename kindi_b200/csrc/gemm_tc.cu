@@ -1,0 +1,222 @@
+// bfloat16 matrix products on the 5th-generation tensor cores: C = A W^T with both operands K-major.
+//
+// One CTA computes a 128 x BN tile of D = P Q^T, where P ("the 128-row side") and Q ("the BN-row side") are
+// [rows][K] bf16 tensors read by TMA (boxes of 64 K-elements, 128-byte swizzle, zero fill past the edges, no
+// multicast) into a ring of shared-memory stages; one elected thread issues tcgen05.mma (M 128, N BN, K 16, fp32
+// accumulator in tensor memory); tcgen05.commit frees a stage when its MMAs are done; four epilogue warps read the
+// accumulator with tcgen05.ld and write C.
+//   - prefill form: P = activations (tokens), Q = weights (features): a TMEM lane is a token, a column a feature.
+//   - decode form ("swap"): P = weights (128 features a tile), Q = the few activation rows (BN = 16..128 tokens):
+//     the weights stream through the 128-row side at memory speed and the batch is the narrow side.
+// gridDim.z splits K; each split writes its own fp32 partial plane (no atomics: the caller adds the planes in
+// order, so results are the same on every run).
+// The reference's counterparts are its int8 mma.sync prompt product (kindi/nbq_mm.cu:23-178) and its dp4a
+// matrix-vector products (kindi/nbq.cu:266-296).
+#include "sm100.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192          // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+
+template <int BN, int STAGES>
+struct TcSmem {
+    static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+    static constexpr int B_BYTES = BN * TC_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;     // + alignment slack
+};
+
+template <int BN, int STAGES, bool SWAP, typename TC>
+__global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ CUtensorMap mapP,
+        const __grid_constant__ CUtensorMap mapQ, TC* __restrict__ C, int rowsP, int rowsQ, int K, int ldc,
+        long long split_stride, int kb_per_split, int* status) {
+    using S = TcSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + S::BAR_OFF, bar_empty = bar_full + STAGES * 8, bar_acc = bar_empty + STAGES * 8;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + S::BAR_OFF + (2 * STAGES + 1) * 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = blockIdx.x * TC_BM, q0 = blockIdx.y * BN;
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb0 = blockIdx.z * kb_per_split;
+    const int kb1 = min(total_kb, kb0 + kb_per_split);
+    const int nkb = kb1 - kb0;                      // > 0 by construction of the grid
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        mbar_init(bar_acc, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&mapP);
+        tma_prefetch_desc(&mapQ);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, status)) break;
+                mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
+                const uint32_t dst = sbase + s * S::STAGE_BYTES;
+                tma_load_2d(dst, &mapP, (kb0 + i) * TC_BK, p0, bar_full + s * 8);
+                tma_load_2d(dst + S::A_BYTES, &mapQ, (kb0 + i) * TC_BK, q0, bar_full + s * 8);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; i++) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                ok = mbar_wait(bar_full + s * 8, ph, status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a = sbase + s * S::STAGE_BYTES, b = a + S::A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++)
+                    umma_bf16(tmem, umma_desc_sw128(a + k * 32), umma_desc_sw128(b + k * 32), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar_empty + s * 8);
+            }
+            umma_commit(bar_acc);
+        }
+    } else {
+        // epilogue warps 2..5 own TMEM lanes 32 * (warp % 4) .. + 31
+        const int quarter = warp & 3;
+        const bool ok = mbar_wait(bar_acc, 0, status);
+        tc_fence_after();
+        const int prow = p0 + quarter * 32 + lane;           // row of the 128-row side this thread holds
+        TC* Cz = C + (size_t)blockIdx.z * split_stride;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld_32x16(tmem + ((uint32_t)(quarter * 32) << 16) + c0, r);
+                tmem_ld_wait();
+                if (SWAP) {
+                    // C[token q0 + c][feature prow]: a warp's 32 lanes write 32 consecutive features
+                    if (prow < rowsP) {
+#pragma unroll
+                        for (int c = 0; c < 16; c++)
+                            if (q0 + c0 + c < rowsQ)
+                                Cz[(size_t)(q0 + c0 + c) * ldc + prow] = kb_from_f<TC>(__uint_as_float(r[c]));
+                    }
+                } else {
+                    // C[token prow][feature q0 + c]: each thread writes 16 consecutive features of its row
+                    if (prow < rowsP) {
+                        TC* dst = Cz + (size_t)prow * ldc + q0 + c0;
+                        if (q0 + c0 + 16 <= rowsQ && (((uintptr_t)dst) & 15) == 0) {
+                            if (sizeof(TC) == 4) {
+#pragma unroll
+                                for (int c = 0; c < 16; c += 4)
+                                    *(uint4*)(dst + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
+                            } else {
+                                uint32_t h[8];
+#pragma unroll
+                                for (int c = 0; c < 8; c++) {
+                                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * c]),
+                                                                             __uint_as_float(r[2 * c + 1]));
+                                    h[c] = *(uint32_t*)&v;
+                                }
+                                *(uint4*)(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+                                *(uint4*)(dst + 8) = make_uint4(h[4], h[5], h[6], h[7]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 16; c++)
+                                if (q0 + c0 + c < rowsQ) dst[c] = kb_from_f<TC>(__uint_as_float(r[c]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+template <int BN, int STAGES, bool SWAP, typename TC>
+static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int rowsP, int rowsQ, int K, int ldc,
+                     int splits, long long split_stride, int* status, cudaStream_t st) {
+    using S = TcSmem<BN, STAGES>;
+    auto kern = k_gemm_tc<BN, STAGES, SWAP, TC>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    int kbps = (total_kb + splits - 1) / splits;
+    int z = (total_kb + kbps - 1) / kbps;               // every split has at least one k-block
+    dim3 grid((rowsP + TC_BM - 1) / TC_BM, (rowsQ + BN - 1) / BN, z);
+    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(mp, mq, (TC*)C, rowsP, rowsQ, K, ldc, split_stride, kbps, status);
+    return (int)cudaGetLastError();
+}
+
+// how many K splits the launch will use for a wanted number (the caller sizes the partial planes with it)
+extern "C" int kb_gemm_tc_splits(int K, int wanted) {
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    if (wanted < 1) wanted = 1;
+    if (wanted > total_kb) wanted = total_kb;
+    int kbps = (total_kb + wanted - 1) / wanted;
+    return (total_kb + kbps - 1) / kbps;
+}
+
+// C[M][N] (+ split planes) = A[M][K] W[N][K]^T. cdtype: KB_F32 or KB_BF16 (bf16 only without splits).
+// swap = 0: prefill form (tile 128 tokens x bn features); swap = 1: decode form (tile 128 features x bn tokens).
+extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int M, int N, int K, int lda, int ldw,
+                          int ldc, int swap, int bn, int splits, long long split_stride, int* status,
+                          cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((K % 8) || (lda % 8) || (ldw % 8)) return (int)cudaErrorInvalidValue;
+    if (splits > 1 && cdtype != KB_F32) return (int)cudaErrorInvalidValue;
+    CUtensorMap mp, mq;
+    int rc;
+    const void* P = swap ? W : A;
+    const void* Q = swap ? A : W;
+    const int rowsP = swap ? N : M, rowsQ = swap ? M : N;
+    const int ldp = swap ? ldw : lda, ldq = swap ? lda : ldw;
+    if ((rc = kb_make_map_bf16(&mp, P, rowsP, K, ldp, TC_BM))) return rc;
+    if ((rc = kb_make_map_bf16(&mq, Q, rowsQ, K, ldq, bn))) return rc;
+#define TC_GO(BN, ST, SW)                                                                                         \
+    return cdtype == KB_F32                                                                                       \
+               ? launch_tc<BN, ST, SW, float>(mp, mq, C, rowsP, rowsQ, K, ldc, splits, split_stride, status, st)  \
+               : launch_tc<BN, ST, SW, bf16>(mp, mq, C, rowsP, rowsQ, K, ldc, splits, split_stride, status, st)
+    if (swap) {
+        switch (bn) {
+            case 16: TC_GO(16, 8, true);
+            case 32: TC_GO(32, 8, true);
+            case 64: TC_GO(64, 6, true);
+            case 128: TC_GO(128, 5, true);
+            default: return (int)cudaErrorInvalidValue;
+        }
+    } else {
+        switch (bn) {
+            case 64: TC_GO(64, 6, false);
+            case 128: TC_GO(128, 6, false);
+            case 256: TC_GO(256, 4, false);
+            default: return (int)cudaErrorInvalidValue;
+        }
+    }
+#undef TC_GO
+}

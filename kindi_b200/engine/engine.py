@@ -153,6 +153,32 @@ class Engine:
             raise EngineError("a kernel reported: %s (status %d); the step's results are not valid"
                               % ("; ".join(what) or "unknown", st))
 
+    # ------------------------------------------------------------------ generation
+    def generate_batch(self, prompts, params=None, *, on_tokens=None, cancel=None, **options):
+        """generate for a list of prompts (token ids). ``params`` is a ``SamplingParams``; or give its fields as
+        keyword options with the reference's names (``temperature``, ``top_p``, ``top_k``, ``min_p``,
+        ``repeat_penalty``, ``repeat_last_n``, ``max_tokens``, ``seed``, ``stop_token_ids``). Returns a
+        ``GenerationResult`` (``tokens``, ``finish``, ``stats``). The stop tokens are the model's end-of-sequence
+        ids plus the given ones."""
+        from ..config.runtime import SamplingParams
+        from ..sampling.sampler import request_seed
+        from .generate import generate
+        if params is None:
+            params = SamplingParams.from_options(**options)
+        elif options:
+            params = params.with_(**options)
+        stepper = EngineStepper(self, request_seed(params))
+        return generate(stepper, prompts, params, stop_token_ids=self.spec.stop_token_ids, on_tokens=on_tokens,
+                        cancel=cancel)
+
+    def generate(self, ids, n: int):
+        """the greedy continuation of one prompt: exactly ``n`` tokens, stop tokens included, as the reference's
+        ``Engine.generate(ids, n)`` (``kindi/nanbeige.py:1317-1325``)"""
+        from ..config.runtime import SamplingParams
+        from .generate import generate
+        stepper = EngineStepper(self, 0)
+        return generate(stepper, [list(ids)], SamplingParams(temperature=0.0, max_tokens=n)).tokens[0]
+
     # ------------------------------------------------------------------ accounting
     def weight_bytes_per_step(self, n_rows: int) -> int:
         return self.model.bytes_read(n_rows)
@@ -164,3 +190,37 @@ class Engine:
 def _to_run_dtype(t: torch.Tensor, run_dtype: str) -> torch.Tensor:
     from ..weights.loader import target_dtype
     return t.to(target_dtype(t.dtype, run_dtype))
+
+
+class EngineStepper:
+    """what the generation loop drives: the engine's step followed by the sampler, one host read per step"""
+
+    def __init__(self, engine: Engine, seed: int):
+        from ..sampling.sampler import Sampler
+        self.engine = engine
+        self.ctx = engine.ctx
+        self.max_batch = engine.max_batch
+        self.sampler = Sampler(engine.device)
+        self.seed = seed
+        self._rng: Dict[int, object] = {}
+
+    def alloc(self) -> int:
+        return self.engine.alloc()
+
+    def free(self, slot: int) -> None:
+        self.engine.free(slot)
+
+    def run(self, entries, params, seq_ids, histories) -> List[int]:
+        from ..sampling.sampler import SequenceRandom
+        logits = self.engine.step(entries)
+        uniforms = None
+        if not params.greedy:
+            uniforms = []
+            for sid in seq_ids:
+                if sid not in self._rng:
+                    self._rng[sid] = SequenceRandom(self.seed, sid)
+                uniforms.append(self._rng[sid].next())
+        picked = self.sampler.pick(logits, params, uniforms, histories if params.repeat_penalty != 1.0 else None)
+        toks = picked.tolist()
+        self.engine.check_status()
+        return toks

@@ -1,0 +1,140 @@
+"""The generation loop above the step function.
+
+Requests are taken in order and formed into batches that start together: all prompts of a batch run in one step,
+then every live sequence brings one token a step. A sequence ends at a stop token (which is not part of its
+output, ``kindi/nanbeige_gen.py:272-274``) or when it has ``max_new`` tokens, where ``max_new = max(1,
+min(max_tokens, ctx - len(prompt)))`` and a prompt of ``ctx`` tokens or more is refused
+(``kindi/nanbeige_gen.py:210-212,219-220``). A sequence that ends leaves the batch and gives back its slot at once;
+when the batch is empty the next one starts, in slots and pages that were used before. The reference serves one
+request at a time (``kindi/nanbeige_gen.py:261-283``); batches are this library's own.
+
+The loop's decisions need no GPU: it talks to a *stepper* (``alloc``, ``free``, ``run``), which is the engine in
+production and a stand-in in the CPU tests.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+from ..cache.pages import PAGE, pages_for
+from ..config.runtime import SamplingParams
+from .batch import StepEntry
+
+
+class PromptTooLong(ValueError):
+    """the prompt alone fills the context (the reference's ContextOverflow, ``kindi/server.py:26-36``)"""
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prompt_s: float = 0.0
+    gen_s: float = 0.0
+    steps: int = 0
+    batches: int = 0
+
+    @property
+    def gen_tok_s(self) -> float:
+        return self.generated_tokens / self.gen_s if self.gen_s > 0 else 0.0
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[List[int]]
+    finish: List[str]                       # "stop" | "length" per request
+    stats: GenerationStats = field(default_factory=GenerationStats)
+
+
+def max_new_tokens(prompt_len: int, max_tokens: int, ctx: int) -> int:
+    if prompt_len < 1:
+        raise ValueError("a prompt needs at least one token")
+    if prompt_len >= ctx:
+        raise PromptTooLong("the prompt has %d tokens and the context holds %d: nothing could be generated"
+                            % (prompt_len, ctx))
+    return max(1, min(max_tokens, ctx - prompt_len))
+
+
+def plan_batches(prompt_lens: Sequence[int], max_new: Sequence[int], ctx: int, max_batch: int) -> List[List[int]]:
+    """request indices per batch, in order. A batch takes requests while it has room for another sequence and the
+    cache can hold every member at its greatest possible length (prompt + max_new - 1 stored tokens, rounded up to
+    a page each), so that a started batch can never run out of pages."""
+    room = pages_for(ctx)
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    used = 0
+    for i, (p, m) in enumerate(zip(prompt_lens, max_new)):
+        need = pages_for(p + m - 1)
+        if need > room:
+            raise PromptTooLong("request %d needs %d tokens of cache and the context holds %d" % (i, need * PAGE, ctx))
+        if cur and (len(cur) >= max_batch or used + need > room):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def generate(stepper, prompts: Sequence[Sequence[int]], params: SamplingParams, *,
+             stop_token_ids: Sequence[int] = (), on_tokens: Optional[Callable[[Dict[int, int]], None]] = None,
+             cancel: Optional[Callable[[], bool]] = None) -> GenerationResult:
+    """generate for every prompt; returns the new tokens of each (without the stop token).
+
+    ``stepper`` offers ``ctx``, ``max_batch``, ``alloc()``, ``free(slot)`` and ``run(entries, params, seq_ids,
+    histories) -> [token per entry]`` (each entry wants exactly one place). ``on_tokens`` is called after each step
+    with {request index: new token}; ``cancel()`` true ends all live sequences with finish "stop"
+    (``kindi/nanbeige_gen.py:265-267``)."""
+    stop = set(int(t) for t in stop_token_ids) | set(int(t) for t in params.stop_token_ids)
+    n = len(prompts)
+    prompts = [list(int(t) for t in p) for p in prompts]
+    max_new = [max_new_tokens(len(p), params.max_tokens, stepper.ctx) for p in prompts]
+    batches = plan_batches([len(p) for p in prompts], max_new, stepper.ctx, stepper.max_batch)
+    out: List[List[int]] = [[] for _ in range(n)]
+    finish: List[str] = ["length"] * n
+    stats = GenerationStats(prompt_tokens=sum(len(p) for p in prompts), batches=len(batches))
+    for batch in batches:
+        slots = {i: stepper.alloc() for i in batch}
+        live = list(batch)
+        try:
+            t0 = time.perf_counter()
+            entries = [StepEntry(slots[i], tuple(prompts[i]), (len(prompts[i]) - 1,)) for i in live]
+            toks = stepper.run(entries, params, live, [prompts[i] for i in live])
+            stats.prompt_s += time.perf_counter() - t0
+            stats.steps += 1
+            t0 = time.perf_counter()
+            while True:
+                nxt: List[int] = []
+                emitted: Dict[int, int] = {}
+                for i, t in zip(live, toks):
+                    t = int(t)
+                    if t in stop:
+                        finish[i] = "stop"
+                    else:
+                        out[i].append(t)
+                        emitted[i] = t
+                        if len(out[i]) < max_new[i]:
+                            nxt.append(i)
+                            continue
+                        finish[i] = "length"
+                    stepper.free(slots.pop(i))
+                stats.generated_tokens += len(emitted)
+                if on_tokens is not None and emitted:
+                    on_tokens(emitted)
+                if cancel is not None and nxt and cancel():
+                    for i in nxt:
+                        finish[i] = "stop"
+                    nxt = []
+                live = nxt
+                if not live:
+                    break
+                entries = [StepEntry(slots[i], (out[i][-1],), (0,)) for i in live]
+                toks = stepper.run(entries, params, live, [prompts[i] + out[i] for i in live])
+                stats.steps += 1
+            stats.gen_s += time.perf_counter() - t0
+        finally:
+            for s in slots.values():
+                stepper.free(s)
+    return GenerationResult(out, finish, stats)

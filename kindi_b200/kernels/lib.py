@@ -38,6 +38,12 @@ _SIGS = {
     "kb_attn_generic": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "kb_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                   c_longlong, c_void_p, c_void_p],
+    "kb_gemm_tc_splits": [c_int, c_int],
+    "kb_sample": [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
+                  c_void_p],
+    "kb_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_float, c_void_p],
 }
 
 
@@ -174,3 +180,26 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
     T, F = out.shape
     assert gu.shape == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype
     _check(load().kb_swiglu(_p(gu), _p(out), dt(gu), T, F, _stream()), "swiglu")
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,
+            status: torch.Tensor) -> None:
+    """out = a[M, K] @ w[N, K]^T on the tensor cores (bf16 in, fp32 accumulate). ``out`` is [M, N] (bf16 or fp32)
+    or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits)"""
+    _need_cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.is_contiguous()
+    if out.dim() == 3:
+        assert out.shape == (gemm_tc_splits(K, splits), M, N) and out.dtype == torch.float32
+        stride = M * N
+    else:
+        assert out.shape == (M, N) and splits == 1
+        stride = 0
+    _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), N, 1 if swap else 0,
+                             bn, splits, stride, _p(status), _stream()), "gemm_tc")
+
+
+def gemm_tc_splits(K: int, wanted: int) -> int:
+    return load().kb_gemm_tc_splits(K, wanted)
