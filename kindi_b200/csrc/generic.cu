@@ -175,16 +175,19 @@ extern "C" int kb_gemm_simt(const void* A, int adtype, const void* W, int wdtype
 // copied there. The rotation pairs element i with i + rot/2 (i < rot/2; elements from rot on pass through); the
 // angle is (float)pos * inv_freq[i] in 32-bit, cosine and sine by the accurate library functions, and the four
 // products are rounded one by one (kindi/nbq.cu:127-130).
-template <typename T>
-__global__ void k_rope_store(T* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rot,
+template <typename TIN, typename T>
+__global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t plane_stride, int ld_in,
+        T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
         const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
         int hd, KbCacheView cv, int* status) {
     const int t = blockIdx.x, h = blockIdx.y;
     const int p = pos[t];
-    T* src = qkv + (size_t)t * ld + (size_t)h * hd;
-    T* dst = src;
+    const TIN* src = in + (size_t)t * ld_in + (size_t)h * hd;
+    T* dst;
     const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
-    if (!is_q) {
+    if (is_q) {
+        dst = qout + (size_t)t * ldq + (size_t)h * hd;
+    } else {
         const int hk = is_k ? h - nh : h - nh - nkv;
         const int s = slot[seq[t]];
         const int page = cv.table[(size_t)s * cv.table_stride + p / KB_PAGE];
@@ -194,33 +197,45 @@ __global__ void k_rope_store(T* __restrict__ qkv, int ld, const float* __restric
         }
         dst = (T*)cv.pool + kb_kv_offset(cv, page, is_k ? 0 : 1, hk, p % KB_PAGE);
     }
+    auto rd = [&](int i) {
+        float v = kb_to_f<TIN>(src[i]);
+        for (int s = 1; s < n_planes; s++) v += kb_to_f<TIN>(src[(size_t)s * plane_stride + i]);
+        return v;
+    };
     const int half = rot / 2;
     if (is_q || is_k) {
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float ang = __fmul_rn((float)p, inv_freq[i]);
-            const float c = cosf(ang), s = sinf(ang);
-            const float a = kb_to_f<T>(src[i]), b = kb_to_f<T>(src[i + half]);
-            dst[i] = kb_from_f<T>(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
-            dst[i + half] = kb_from_f<T>(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
+            const float c = cosf(ang), sn = sinf(ang);
+            const float a = rd(i), b = rd(i + half);
+            dst[i] = kb_from_f<T>(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
+            dst[i + half] = kb_from_f<T>(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn)));
         }
-        if (dst != src)
-            for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+        if ((const void*)dst != (const void*)src || n_planes > 1)
+            for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = kb_from_f<T>(rd(i));
     } else {
-        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = kb_from_f<T>(rd(i));
     }
 }
 
-extern "C" int kb_rope_store(void* qkv, int dtype, int ld, const float* inv_freq, int rot, const int* pos,
+// in: [n_planes][T][ld_in] (the planes are summed in order); in_dtype may be 32-bit planes with a bf16 cache / qout
+extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in,
+                             void* qout, int dtype, int ldq, const float* inv_freq, int rot, const int* pos,
                              const int* seq, const int* slot, int T, int nh, int nkv, int hd, void* pool,
                              const int* table, int table_stride, int n_pages, int* status, cudaStream_t st) {
     if (T <= 0) return 0;
     KbCacheView cv{pool, table, table_stride, n_pages, nkv, hd};
     dim3 grid(T, nh + 2 * nkv);
     int thr = hd / 2 < 32 ? 32 : (hd / 2 > 128 ? 128 : ((hd / 2 + 31) / 32) * 32);
-    if (dtype == KB_F32)
-        k_rope_store<float><<<grid, thr, 0, st>>>((float*)qkv, ld, inv_freq, rot, pos, seq, slot, nh, nkv, hd, cv, status);
-    else
-        k_rope_store<bf16><<<grid, thr, 0, st>>>((bf16*)qkv, ld, inv_freq, rot, pos, seq, slot, nh, nkv, hd, cv, status);
+#define KB_RS(TIN, T_)                                                                                        \
+    k_rope_store<TIN, T_><<<grid, thr, 0, st>>>((const TIN*)in, n_planes, (size_t)plane_stride, ld_in,        \
+                                                (T_*)qout, ldq, inv_freq, rot, pos, seq, slot, nh, nkv, hd,   \
+                                                cv, status)
+    if (in_dtype == KB_F32 && dtype == KB_F32) KB_RS(float, float);
+    else if (in_dtype == KB_F32 && dtype == KB_BF16) KB_RS(float, bf16);
+    else if (in_dtype == KB_BF16 && dtype == KB_BF16) KB_RS(bf16, bf16);
+    else return (int)cudaErrorInvalidValue;
+#undef KB_RS
     KB_LAUNCH_RET();
 }
 
@@ -317,21 +332,33 @@ extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int
 
 // ------------------------------------------------------------------------------------------------ SwiGLU
 // gu: [T][2F] = gate then up; out[t][i] = gate / (1 + exp(-gate)) * up (kindi/nbq.cu:461-467)
-template <typename T>
-__global__ void k_swiglu(const T* __restrict__ gu, T* __restrict__ out, int F, long long total) {
+template <typename TIN, typename T>
+__global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_stride, T* __restrict__ out, int F,
+                         long long total) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / F;
     const int c = (int)(i % F);
-    const float g = kb_to_f<T>(gu[t * 2 * F + c]), u = kb_to_f<T>(gu[t * 2 * F + F + c]);
+    float g = 0.0f, u = 0.0f;
+    for (int s = 0; s < n_planes; s++) {
+        g += kb_to_f<TIN>(gu[(size_t)s * plane_stride + t * 2 * F + c]);
+        u += kb_to_f<TIN>(gu[(size_t)s * plane_stride + t * 2 * F + F + c]);
+    }
     out[i] = kb_from_f<T>(g / (1.0f + expf(-g)) * u);
 }
 
-extern "C" int kb_swiglu(const void* gu, void* out, int dtype, int T, int F, cudaStream_t st) {
+// gu: [n_planes][T][2F] (planes summed in order), 32-bit or the output's type
+extern "C" int kb_swiglu(const void* gu, int in_dtype, int n_planes, long long plane_stride, void* out, int dtype,
+                         int T, int F, cudaStream_t st) {
     long long total = (long long)T * F;
     if (total <= 0) return 0;
     int grid = (int)((total + 255) / 256);
-    if (dtype == KB_F32) k_swiglu<float><<<grid, 256, 0, st>>>((const float*)gu, (float*)out, F, total);
-    else k_swiglu<bf16><<<grid, 256, 0, st>>>((const bf16*)gu, (bf16*)out, F, total);
+    if (in_dtype == KB_F32 && dtype == KB_F32)
+        k_swiglu<float, float><<<grid, 256, 0, st>>>((const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total);
+    else if (in_dtype == KB_F32 && dtype == KB_BF16)
+        k_swiglu<float, bf16><<<grid, 256, 0, st>>>((const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
+    else if (in_dtype == KB_BF16 && dtype == KB_BF16)
+        k_swiglu<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
+    else return (int)cudaErrorInvalidValue;
     KB_LAUNCH_RET();
 }

@@ -1,5 +1,5 @@
 """The bfloat16 serving kernels (tensor-core matrix products, tiled attention) and the rules for when each may
-run. Every function returns False / None when its kernel does not take the given shape, and the caller uses the
+run. Every function returns False / None when its kernel does not take the given operands, and the caller uses the
 general kernel instead; nothing here falls back to library code."""
 from __future__ import annotations
 
@@ -7,13 +7,61 @@ from typing import Optional
 
 import torch
 
+from . import lib as K
 
-def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-    return False
+N_SM = 148                 # B200: 2 dies x 74 SMs
+SMALL_M = 128              # up to here the weights go through the 128-row side of the MMA ("swap" form)
 
 
-def gemm_bf16_branch(a: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
-    return None
+def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """what the TMA maps need: bf16, unit inner stride, 16-byte aligned bases and row strides"""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def _swap_bn(m: int) -> int:
+    return 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
+
+
+def wants_planes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return a.shape[0] <= SMALL_M and _tc_ok(a, w)
+
+
+def _splits_for(m: int, n: int, k: int, bn: int) -> int:
+    """enough CTAs to keep every SM streaming weights: about two per SM, each with at least two K blocks"""
+    tiles = -(-n // 128) * -(-m // bn)
+    total_kb = -(-k // 64)
+    want = max(1, min(total_kb // 2, round(2 * N_SM / tiles)))
+    return want
+
+
+def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
+    if not _tc_ok(a, w) or not out.is_contiguous():
+        return False
+    m, n = a.shape[0], w.shape[0]
+    if m <= SMALL_M:
+        K.gemm_tc(a, w, out, swap=True, bn=_swap_bn(m), splits=1, status=status)
+    else:
+        K.gemm_tc(a, w, out, swap=False, bn=256 if n >= 512 else 128 if n > 64 else 64, splits=1, status=status)
+    return True
+
+
+def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optional[torch.Tensor]:
+    if not _tc_ok(a, w):
+        return None
+    m, k = a.shape
+    n = w.shape[0]
+    if m <= SMALL_M:
+        bn = _swap_bn(m)
+        want = _splits_for(m, n, k, bn)
+        s = K.gemm_tc_splits(k, want)
+        out = torch.empty((s, m, n), dtype=torch.float32, device=a.device)
+        K.gemm_tc(a, w, out, swap=True, bn=bn, splits=want, status=status)
+        return out
+    out = torch.empty((1, m, n), dtype=torch.float32, device=a.device)
+    K.gemm_tc(a, w, out[0], swap=False, bn=256 if n >= 512 else 128 if n > 64 else 64, splits=1, status=status)
+    return out
 
 
 def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages) -> bool:

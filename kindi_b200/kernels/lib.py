@@ -33,11 +33,12 @@ _SIGS = {
                        c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_void_p],
-    "kb_rope_store": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                      c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "kb_rope_store": [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                      c_void_p],
     "kb_attn_generic": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
-    "kb_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_longlong, c_void_p, c_void_p],
     "kb_gemm_tc_splits": [c_int, c_int],
@@ -147,18 +148,22 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                out.stride(0), _stream()), "gemm_simt")
 
 
-def rope_store(qkv: torch.Tensor, inv_freq: torch.Tensor, rot: int, pos, seq, slot, nh: int, nkv: int, hd: int,
-               pool: Optional[torch.Tensor], table: torch.Tensor, n_pages: int, status: torch.Tensor) -> None:
-    """rotate the query heads of qkv ([T, (nh + 2 nkv) hd]) in place, rotate and store keys, store values"""
-    _need_cuda(qkv, inv_freq, pool, table)
-    T = qkv.shape[0]
-    assert qkv.stride(1) == 1 and inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot // 2
-    assert rot % 2 == 0 and rot <= hd
+def rope_store(qkv: torch.Tensor, qout: torch.Tensor, inv_freq: torch.Tensor, rot: int, pos, seq, slot, nh: int,
+               nkv: int, hd: int, pool: Optional[torch.Tensor], table: torch.Tensor, n_pages: int,
+               status: torch.Tensor) -> None:
+    """qkv: [T, (nh + 2 nkv) hd], or 32-bit planes [S, T, ...] that are summed. Query heads are rotated into qout
+    ([T, >= nh hd]; may be qkv itself), keys are rotated and stored in the cache, values are stored"""
+    _need_cuda(qkv, qout, inv_freq, pool, table)
+    planes = qkv.shape[0] if qkv.dim() == 3 else 1
+    T = qkv.shape[-2]
+    assert qkv.stride(-1) == 1 and inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(1, rot // 2)
+    assert rot % 2 == 0 and rot <= hd and qout.stride(1) == 1
     if pool is not None:
-        assert pool.dtype == qkv.dtype and pool.is_contiguous()
-    _check(load().kb_rope_store(_p(qkv), dt(qkv), qkv.stride(0), _p(inv_freq), rot, _p(pos), _p(seq), _p(slot), T,
-                                nh, nkv, hd, _p(pool), _p(table), table.stride(0), n_pages, _p(status), _stream()),
-           "rope_store")
+        assert pool.dtype == qout.dtype and pool.is_contiguous()
+    pstride = qkv.stride(0) if qkv.dim() == 3 else 0
+    _check(load().kb_rope_store(_p(qkv), dt(qkv), planes, pstride, qkv.stride(-2), _p(qout), dt(qout),
+                                qout.stride(0), _p(inv_freq), rot, _p(pos), _p(seq), _p(slot), T, nh, nkv, hd,
+                                _p(pool), _p(table), table.stride(0), n_pages, _p(status), _stream()), "rope_store")
 
 
 def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nkv: int, hd: int, scale: float,
@@ -175,11 +180,12 @@ def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nk
 
 
 def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
-    """out[T, F] = silu(gu[:, :F]) * gu[:, F:]"""
+    """out[T, F] = silu(g) * u with [g | u] = gu [T, 2F], or the sum of 32-bit planes gu [S, T, 2F]"""
     _need_cuda(gu, out)
     T, F = out.shape
-    assert gu.shape == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype
-    _check(load().kb_swiglu(_p(gu), _p(out), dt(gu), T, F, _stream()), "swiglu")
+    planes = gu.shape[0] if gu.dim() == 3 else 1
+    assert gu.shape[-2:] == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous()
+    _check(load().kb_swiglu(_p(gu), dt(gu), planes, T * 2 * F, _p(out), dt(out), T, F, _stream()), "swiglu")
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,

@@ -2,37 +2,43 @@
 matrices, ``kindi/nbq.cu:266-296``): the choice of kernel by dtype and shape.
 
 float32 operands always run the fixed-order 32-bit kernel (no tensor cores: the true 32-bit path). bfloat16
-operands run the tcgen05 kernels where their shape rules hold, else the general kernel.
+operands run the tcgen05 kernel where its alignment rules hold, else the general kernel. Nothing here calls a
+library product.
 """
 from __future__ import annotations
 
 import torch
 
+from . import fast
 from . import lib as K
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def linear(ctx, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """a [M, K] @ w [N, K]^T -> [M, N] in out_dtype"""
     out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype, device=a.device)
-    linear_into(a, w, out)
+    if not (ctx.fast and fast.gemm_rows(a, w, out, ctx.status)):
+        K.gemm_simt(a, w, out)
     return out
 
 
-def linear_into(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        from . import fast
-        if fast.gemm_bf16(a, w, out):
-            return
-    K.gemm_simt(a, w, out)
-
-
-def branch(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """a branch output: 32-bit partial sums [S, M, N] whose sum over S (in order) is a @ w^T"""
-    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        from . import fast
-        parts = fast.gemm_bf16_branch(a, w)
-        if parts is not None:
-            return parts
+def planes(ctx, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """a @ w^T as 32-bit partial sums [S, M, N]: their sum over S, taken in order, is the product. The consumers
+    (the next norm for a branch, the rotary/store and SwiGLU kernels) add the planes themselves, so a product that
+    is split over K for the sake of parallelism needs no pass of its own to be reduced"""
+    if ctx.fast:
+        p = fast.gemm_planes(a, w, ctx.status)
+        if p is not None:
+            return p
     out = torch.empty((1, a.shape[0], w.shape[0]), dtype=torch.float32, device=a.device)
     K.gemm_simt(a, w, out[0])
     return out
+
+
+def rows_or_planes(ctx, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """the product for a consumer that takes either form: 32-bit planes when the step is small (so that K can be
+    split), else rows in out_dtype"""
+    if ctx.fast and fast.wants_planes(a, w):
+        p = fast.gemm_planes(a, w, ctx.status)
+        if p is not None:
+            return p
+    return linear(ctx, a, w, out_dtype)

@@ -61,20 +61,23 @@ class CausalSelfAttention(Mixer):
         nh, nkv, hd = self.nh, self.nkv, self.hd
         entry = ctx.entry
         reads_other = entry is not None and entry.reads_cache_of is not None
+        n_q = nh * hd
         if reads_other:
-            qkv = L.linear(y, self.wqkv[: nh * hd], self.dtype)
+            qkv = L.rows_or_planes(ctx, y, self.wqkv[:n_q], self.dtype)
             pool, table, n_pages = ctx.cache.kv_view(entry.reads_cache_of)
-            K.rope_store(qkv, self.position.inv_freq, self.position.rotary_dim, ctx.pos, ctx.seq, ctx.slot, nh, 0,
-                         hd, None, table, n_pages, ctx.status)
+            store_kv = 0
         else:
-            qkv = L.linear(y, self.wqkv, self.dtype)
+            qkv = L.rows_or_planes(ctx, y, self.wqkv, self.dtype)
             pool, table, n_pages = ctx.cache.kv_view(entry.cache)
-            K.rope_store(qkv, self.position.inv_freq, self.position.rotary_dim, ctx.pos, ctx.seq, ctx.slot, nh,
-                         nkv, hd, pool, table, n_pages, ctx.status)
-        att = torch.empty((ctx.T, nh * hd), dtype=self.dtype, device=y.device)
+            store_kv = nkv
+        # 32-bit planes are summed, rotated and written out as rows; rows are rotated in place
+        q = qkv if qkv.dim() == 2 else torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
+        K.rope_store(qkv, q, self.position.inv_freq, self.position.rotary_dim, ctx.pos, ctx.seq, ctx.slot, nh,
+                     store_kv, hd, pool if store_kv else None, table, n_pages, ctx.status)
+        att = torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
         from ..kernels import attention as A
-        A.attention(ctx, qkv, att, nh, nkv, hd, self.scale, self.window, pool, table, n_pages)
-        return Branch(L.branch(att, self.wo))
+        A.attention(ctx, q, att, nh, nkv, hd, self.scale, self.window, pool, table, n_pages)
+        return Branch(L.planes(ctx, att, self.wo))
 
     def bytes_read(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.wqkv, self.wo))

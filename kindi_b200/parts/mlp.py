@@ -33,15 +33,10 @@ class SwiGLU(FeedForward):
         self.wd = weights("down_proj.weight")
 
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:
-        from ..kernels import fast
-        if ctx.fast:
-            h = fast.gate_up_swiglu(y, self)
-            if h is not None:
-                return Branch(L.branch(h, self.wd))
-        gu = L.linear(y, self.wgu, self.dtype)
+        gu = L.rows_or_planes(ctx, y, self.wgu, self.dtype)
         h = torch.empty((y.shape[0], self.f), dtype=self.dtype, device=y.device)
         K.swiglu(gu, h)
-        return Branch(L.branch(h, self.wd))
+        return Branch(L.planes(ctx, h, self.wd))
 
     def bytes_read(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.wgu, self.wd))

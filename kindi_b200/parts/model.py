@@ -66,7 +66,7 @@ class DecoderModel:
         if rows is None or rows.numel() == 0:
             return None
         y = self.final_norm.add_norm(ctx, x, pending, rows=rows)
-        return L.linear(y, self.head, torch.float32)
+        return L.linear(ctx, y, self.head, torch.float32)
 
     def bytes_read(self, n_rows: int) -> int:
         """weight bytes one step reads: every scheduled layer once, the head once, n_rows embedding rows"""
