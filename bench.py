@@ -1,0 +1,278 @@
+#!/usr/bin/env python3
+"""Measurement: decoded tokens a second of the 3B-shaped Nanbeige/Llama-arch model on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
+
+The default run has the layer sizes of the benchmark's 3B-shaped configuration (32 layers, width 2560, 20 heads,
+4 key/value heads of size 128, feed-forward 10496, vocabulary 166144, bfloat16) with seeded random weights, a batch
+of 8 sequences each at a context of 8192 tokens. A "step" is one decode step of the whole batch. It prints ONE JSON
+line: ``value`` = decoded tokens a second timed on the device with CUDA events around exactly K steps; ``e2e`` = the
+same through the Python entry point the generation loop uses, with the step's tokens copied from pinned host memory
+and the picked tokens read back every step; ``prefill`` = one 2048-token prompt; ``roofline`` = the bytes a decode
+step has to read (every weight once, the live sequences' keys and values) over its time, against the measured
+copy bandwidth; ``points`` = decoding at batch 1 and 64. For more than one GPU it says so and exits with 2: this
+library runs on one GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# the benchmark's 3B-shaped configuration
+CONFIG_3B = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=166144, hidden_size=2560,
+                 intermediate_size=10496, num_hidden_layers=32, num_attention_heads=20, num_key_value_heads=4,
+                 head_dim=128, rms_norm_eps=1e-5, rope_theta=70000000.0, tie_word_embeddings=False)
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            with open(p) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            out.update({k: float(v) for k, v in d.items() if k in out and isinstance(v, (int, float))})
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    out = dict(FALLBACK_PEAKS)
+    out["source"] = "fallback"
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while a timed region runs"""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", "0", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                       "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+            out, _ = self.p.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_engine(layers: int, ctx: int, max_batch: int):
+    import torch
+    from kindi_b200.config import ModelConfig, architecture
+    from kindi_b200.engine.engine import Engine
+    from kindi_b200.parts.model import expected_tensors
+    from kindi_b200.weights.random_init import random_tensors
+    cfg = dict(CONFIG_3B)
+    cfg["num_hidden_layers"] = layers
+    mc = ModelConfig.from_dict(cfg)
+    spec = architecture(mc.architecture).build_spec(mc)
+    tensors = random_tensors(expected_tensors(spec), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
+    eng = Engine(spec=spec, tensors=tensors, ctx=ctx, dtype="bfloat16", max_batch=max_batch)
+    eng.config = mc
+    return eng
+
+
+def prefill_flops(mc, T: int) -> float:
+    E, F, nh, nkv, hd, L = (mc.hidden_size, mc.intermediate_size, mc.num_attention_heads, mc.num_key_value_heads,
+                            mc.head_dim, mc.num_hidden_layers)
+    per_tok = 2.0 * (E * (nh + 2 * nkv) * hd + nh * hd * E + 3 * E * F)
+    attn = 2.0 * 2.0 * nh * hd * (T * (T + 1) / 2.0)           # QK^T and PV over the causal half
+    return L * (T * per_tok + attn) + 2.0 * E * mc.vocab_size  # the head runs on one row
+
+
+def bench_prefill(eng, warmup: int, iters: int):
+    import random
+    import torch
+    from kindi_b200.engine.batch import StepEntry
+    rng = random.Random(3)
+    ids = tuple(rng.randrange(eng.spec.vocab_size) for _ in range(PREFILL_TOKENS))
+    times = []
+    for i in range(warmup + iters):
+        slot = eng.alloc()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([StepEntry(slot, ids, (PREFILL_TOKENS - 1,))])
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+        eng.free(slot)
+    eng.check_status()
+    return statistics.median(times)
+
+
+def fill_context(eng, batch: int, context: int):
+    """B sequences that each hold `context` tokens: pages are mapped and lengths set; the keys and values are
+    synthetic (the whole pool is filled with N(0, 1) once), which costs a decode step exactly what real ones do"""
+    slots = []
+    for _ in range(batch):
+        s = eng.alloc()
+        eng.cache.reserve(s, context)
+        eng.cache.commit(s, context)
+        slots.append(s)
+    eng.cache.flush()
+    return slots
+
+
+def bench_decode(eng, batch: int, context: int, steps: int, warmup: int, e2e: bool):
+    """returns (device ms per step, e2e ms per step or None, launches in the device-timed region, bytes per step)"""
+    import torch
+    from kindi_b200.config.runtime import SamplingParams
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.engine.engine import EngineStepper
+    from kindi_b200.kernels import lib as K
+    slots = fill_context(eng, batch, context - 1)
+    greedy = SamplingParams(temperature=0.0, max_tokens=1)
+    stepper = EngineStepper(eng, 0)
+    toks = [(17 * i + 5) % eng.spec.vocab_size for i in range(batch)]
+    seq_ids = list(range(batch))
+
+    def one(toks):
+        entries = [StepEntry(s, (t,), (0,)) for s, t in zip(slots, toks)]
+        return stepper.sampler.pick(eng.step(entries), greedy)
+
+    for _ in range(max(3, warmup)):
+        one(toks)
+    torch.cuda.synchronize()
+    eng.check_status()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = K.launch_count()
+    a.record()
+    for _ in range(steps):
+        one(toks)
+    b.record()
+    torch.cuda.synchronize()
+    dev_ms = a.elapsed_time(b) / steps
+    launches = K.launch_count() - n0
+    eng.check_status()
+    e2e_ms = None
+    if e2e:
+        cur = toks
+        for _ in range(3):
+            cur = stepper.run([StepEntry(s, (t,), (0,)) for s, t in zip(slots, cur)], greedy, seq_ids, None)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            cur = stepper.run([StepEntry(s, (t,), (0,)) for s, t in zip(slots, cur)], greedy, seq_ids, None)
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1000.0 / steps
+    length = eng.length(slots[0])
+    bytes_step = eng.weight_bytes_per_step(batch) + batch * context * eng.kv_bytes_per_token()
+    for s in slots:
+        eng.free(s)
+    return dev_ms, e2e_ms, launches, bytes_step
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=CONFIG_3B["num_hidden_layers"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    a = ap.parse_args(argv)
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "ahtx/kindi's Nanbeige engine needs CuPy (not installed, no index) and a quantised GGUF "
+                          "model file; it has no bf16 safetensors path and serves one request at a time"}))
+        return 0
+    if a.gpus != 1:
+        print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
+        return 2
+    a.warmup = max(3, a.warmup)
+    import torch
+    from kindi_b200.engine.batch import layout
+    pk = peaks()
+    max_b = max(a.batch, 1 if a.no_points else 64)
+    ctx = max_b * (a.context + a.steps * 2 + a.warmup + 256) + PREFILL_TOKENS + 64
+    eng = build_engine(a.layers, ctx, max_b)
+    for g in eng.cache.groups:
+        g.pool.normal_(0.0, 1.0)
+    mc = eng.config
+    clocks = ClockSampler()
+    clocks.start()
+    dev_ms, e2e_ms, launches, bytes_step = bench_decode(eng, a.batch, a.context, a.steps, a.warmup, True)
+    clk = clocks.stop()
+    value = a.batch * 1000.0 / dev_ms
+    out = {
+        "metric": "decode tokens/s (batch %d, context %d)" % (a.batch, a.context), "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(dev_ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02) seed 0, synthetic token ids, cache filled with N(0,1)",
+        "impl": "ours",
+        "config": {"model": "Nanbeige4-3B-shaped llama-arch", "global_batch": a.batch, "seq_len": a.context,
+                   "parallelism": "none (1 GPU)", "layers": a.layers, "layers_of_config": CONFIG_3B["num_hidden_layers"],
+                   "hidden_size": mc.hidden_size, "heads": mc.num_attention_heads, "kv_heads": mc.num_key_value_heads,
+                   "head_dim": mc.head_dim, "intermediate_size": mc.intermediate_size, "vocab_size": mc.vocab_size,
+                   "rope_theta": mc.rope_theta, "rms_norm_eps": mc.rms_norm_eps, "tied": mc.tie_word_embeddings,
+                   "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2 (a step reads %.1f GB)" % (bytes_step / 1e9),
+                   "cuda_graph": eng.graph_replays > 0},
+        "clocks": clk,
+        "gpu_launches": launches,
+        "e2e": {"value": round(a.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 4 * layout(a.batch, a.batch, a.batch)[1], "d2h_bytes_per_step": 4 * a.batch,
+                "ms_per_step": round(e2e_ms, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(bytes_step / dev_ms / 1e6, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(bytes_step / dev_ms / 1e6 / pk["hbm_gbs"], 4),
+                     "of": pk["source"], "bytes_per_step": int(bytes_step)},
+    }
+    if not a.no_points:
+        T = PREFILL_TOKENS
+        pms = bench_prefill(eng, 3, 5)
+        fl = prefill_flops(mc, T)
+        out["prefill"] = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+                          "frac": round(fl / (pms / 1000.0) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"],
+                          "tflop": round(fl / 1e12, 3)}
+        pts = {}
+        for b in (1, 64):
+            ms, _, _, _ = bench_decode(eng, b, a.context, max(16, a.steps // 2), a.warmup, False)
+            pts["decode_b%d" % b] = round(b * 1000.0 / ms, 1)
+        out["points"] = pts
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,388 @@
+// bfloat16 attention over the paged cache for prefill and for decode.
+//
+// One CTA serves one key/value head of one sequence: its rows are the (token, query head of the group) pairs that
+// read this head, r = token * G + j (the reference packs rows the same way, kindi/nbq_fa.cu:3-5,40-49), so a tile of
+// keys and values is fetched once for all G query heads. Pages of 64 positions are brought in by TMA (two tile loads
+// of 64 columns per 128 bytes of head, 128-byte swizzle, no multicast) by a producer warp into a ring of stages;
+// four consumer warps compute S = Q K^T and O += P V with tensor-core MMAs (bf16 in, fp32 accumulate), softmax in
+// 32-bit with a running maximum and sum (kindi/nbq_fa.cu:31-151: the same flash-attention recurrence).
+//   - prefill form: 64 rows a CTA, 16 a warp; every warp walks all keys up to its rows' own positions.
+//   - decode form: the G rows of one token; the four warps split each page's 64 keys, gridDim.x splits the pages
+//     (kindi/nbq.cu:525-633: position splits and per-warp running maxima), and the parts are merged in a fixed order
+//     (kindi/nbq.cu:635-649).
+// Head sizes 64 and 128; any number of heads and groups for prefill, groups up to 16 for decode. Other shapes run
+// the general kernel.
+#include "sm100.cuh"
+
+#define AT_THREADS 160          // warps 0-3: MMA + softmax, warp 4: TMA producer
+#define AT_ROWS 64              // rows per CTA in the prefill form
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+// byte offset of (row, 16-byte chunk) in a [64 rows][HD] tile stored as HD/64 swizzled boxes of [64][128 bytes]
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * 8192 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+template <int HD, bool DEC>
+__global__ void __launch_bounds__(AT_THREADS) k_attn_mma(const __grid_constant__ CUtensorMap kvmap,
+        const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
+        float* __restrict__ part_ml, const int* __restrict__ slot, const int* __restrict__ q_start,
+        const int* __restrict__ kv_len, int nh, int nkv, int G, float scale_log2e, int window,
+        const int* __restrict__ table, int table_stride, int n_pages, int* status) {
+    constexpr int AT_STAGES = DEC ? 3 : 2;      // pages in flight (two CTAs fit an SM in both forms)
+    constexpr int KT = HD / 16;                 // k-steps of Q K^T
+    constexpr int NT = DEC ? 2 : 8;             // 8-key tiles a warp takes from each page
+    constexpr int DT = HD / 8;                  // 8-column tiles of the output
+    constexpr int TILE_BYTES = 64 * HD * 2;     // one page of keys (or values) of one head
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    constexpr int QS = HD + 8;                  // padded row of the Q staging tile (elements)
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + AT_STAGES * STAGE_BYTES, bar_empty = bar_full + AT_STAGES * 8;
+    // Q staging: [4 warps][16][QS] (prefill); one shared [16][QS] for decode, where every warp has the same rows and
+    // writes the same values
+    bf16* qs = (bf16*)(smem + AT_STAGES * STAGE_BYTES + 2 * AT_STAGES * 8 + 16);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, hk = blockIdx.y;
+    const int qs0 = q_start[b], qlen = q_start[b + 1] - qs0, kvl = kv_len[b];
+    const int pos0 = kvl - qlen;                 // position of the sequence's first row of this step
+    const int n_rows = qlen * G;
+    int row0, pg_lo, pg_hi;                      // the CTA's first row; its pages [pg_lo, pg_hi]
+    if (DEC) {
+        row0 = 0;
+        const int lo = (window > 0 && kvl - window > 0) ? kvl - window : 0;       // row position is kvl - 1
+        const int first = lo / KB_PAGE, last = (kvl - 1) / KB_PAGE;
+        const int per = (last - first + (int)gridDim.x) / (int)gridDim.x;        // ceil(pages / splits)
+        pg_lo = first + (int)blockIdx.x * per;
+        pg_hi = min(last, pg_lo + per - 1);
+    } else {
+        const int n_tiles = (n_rows + AT_ROWS - 1) / AT_ROWS;
+        if ((int)blockIdx.x >= n_tiles) return;
+        row0 = (n_tiles - 1 - (int)blockIdx.x) * AT_ROWS;          // the longest tiles first
+        const int last_row = min(n_rows, row0 + AT_ROWS) - 1;
+        const int p_first = pos0 + row0 / G, p_last = pos0 + last_row / G;
+        const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+        pg_lo = lo / KB_PAGE;
+        pg_hi = p_last / KB_PAGE;
+    }
+    const int n_iter = pg_hi - pg_lo + 1;        // may be <= 0 for an empty decode split
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < AT_STAGES; s++) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 4);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // per-thread accumulators (consumer warps)
+    float o[DT][4];
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+#pragma unroll
+    for (int i = 0; i < DT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0 && n_iter > 0) {
+            tma_prefetch_desc(&kvmap);
+            const int* trow = table + (size_t)slot[b] * table_stride;
+            for (int i = 0; i < n_iter; i++) {
+                const int s = i % AT_STAGES;
+                const uint32_t ph = (uint32_t)(i / AT_STAGES) & 1u;
+                if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, status)) break;
+                int page = trow[pg_lo + i];
+                if (page < 0 || page >= n_pages) {
+                    atomicOr(status, KB_ST_BAD_PAGE);
+                    page = 0;
+                }
+                mbar_expect_tx(bar_full + s * 8, STAGE_BYTES);
+                const uint32_t dst = sbase + s * STAGE_BYTES;
+                const int krow = ((page * 2 + 0) * nkv + hk) * KB_PAGE, vrow = ((page * 2 + 1) * nkv + hk) * KB_PAGE;
+#pragma unroll
+                for (int h = 0; h < HD / 64; h++) {
+                    tma_load_2d(dst + h * 8192, &kvmap, h * 64, krow, bar_full + s * 8);
+                    tma_load_2d(dst + TILE_BYTES + h * 8192, &kvmap, h * 64, vrow, bar_full + s * 8);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- consumers
+        // this warp's 16 rows: r = wrow0 + 0..15; thread rows ra = lane / 4, rb = ra + 8
+        const int wrow0 = row0 + (DEC ? 0 : warp * 16);
+        bf16* qw = qs + (DEC ? 0 : warp) * 16 * QS;
+        for (int e = lane; e < 16 * (HD / 8); e += 32) {
+            const int r = e / (HD / 8), c = e % (HD / 8);
+            const int gr = wrow0 + r;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (gr < n_rows) {
+                const int t = gr / G, j = gr % G;
+                v = *(const uint4*)(q + (size_t)(qs0 + t) * ldq + (size_t)(hk * G + j) * HD + c * 8);
+            }
+            *(uint4*)(qw + r * QS + c * 8) = v;
+        }
+        __syncwarp();
+        uint32_t qf[KT][4];
+#pragma unroll
+        for (int ks = 0; ks < KT; ks++) {
+            const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
+            ldsm_x4(smem_u32(qw + r * QS + c * 8), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+        }
+        const int ra = wrow0 + (lane >> 2), rb = ra + 8;
+        const int pa = ra < n_rows ? pos0 + ra / G : -1, pb = rb < n_rows ? pos0 + rb / G : -1;
+        const int la = (window > 0 && pa - window + 1 > 0) ? pa - window + 1 : 0;
+        const int lb = (window > 0 && pb - window + 1 > 0) ? pb - window + 1 : 0;
+        // the last position any row of this warp reads: later pages are skipped by the whole warp
+        int wlast = max(pa, pb);
+        wlast = max(wlast, __shfl_xor_sync(0xffffffffu, wlast, 4));
+        wlast = max(wlast, __shfl_xor_sync(0xffffffffu, wlast, 8));
+        wlast = max(wlast, __shfl_xor_sync(0xffffffffu, wlast, 16));
+        const int kw0 = DEC ? warp * 16 : 0;          // the warp's first key inside a page
+
+        for (int i = 0; i < n_iter; i++) {
+            const int s = i % AT_STAGES;
+            const uint32_t ph = (uint32_t)(i / AT_STAGES) & 1u;
+            if (!mbar_wait(bar_full + s * 8, ph, status)) break;
+            const int key0 = (pg_lo + i) * KB_PAGE + kw0;           // absolute position of the warp's first key
+            if (key0 <= wlast) {
+                const uint32_t kt = sbase + s * STAGE_BYTES, vt = kt + TILE_BYTES;
+                float sc[NT][4];
+#pragma unroll
+                for (int n = 0; n < NT; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+                for (int n2 = 0; n2 < NT / 2; n2++) {
+                    const int krow = kw0 + n2 * 16 + (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+                    for (int ks = 0; ks < KT; ks++) {
+                        uint32_t r0, r1, r2, r3;
+                        ldsm_x4(kt + tile_off(krow, ks * 2 + ((lane >> 3) & 1)), r0, r1, r2, r3);
+                        mma_bf16(sc[2 * n2], qf[ks], r0, r1);
+                        mma_bf16(sc[2 * n2 + 1], qf[ks], r2, r3);
+                    }
+                }
+                // scale, mask, running maximum
+                float mxa = -INFINITY, mxb = -INFINITY;
+#pragma unroll
+                for (int n = 0; n < NT; n++) {
+                    const int p = key0 + n * 8 + (lane & 3) * 2;
+                    sc[n][0] = (p <= pa && p >= la) ? sc[n][0] * scale_log2e : -INFINITY;
+                    sc[n][1] = (p + 1 <= pa && p + 1 >= la) ? sc[n][1] * scale_log2e : -INFINITY;
+                    sc[n][2] = (p <= pb && p >= lb) ? sc[n][2] * scale_log2e : -INFINITY;
+                    sc[n][3] = (p + 1 <= pb && p + 1 >= lb) ? sc[n][3] * scale_log2e : -INFINITY;
+                    mxa = fmaxf(mxa, fmaxf(sc[n][0], sc[n][1]));
+                    mxb = fmaxf(mxb, fmaxf(sc[n][2], sc[n][3]));
+                }
+                mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 1));
+                mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 2));
+                mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 1));
+                mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 2));
+                const float na = fmaxf(m_a, mxa), nb = fmaxf(m_b, mxb);
+                const float ua = na == -INFINITY ? 0.0f : na, ub = nb == -INFINITY ? 0.0f : nb;
+                const float fa = exp2f(m_a - ua), fb = exp2f(m_b - ub);
+                m_a = na;
+                m_b = nb;
+                float sa = 0.0f, sb = 0.0f;
+                uint32_t pf[NT][2];
+#pragma unroll
+                for (int n = 0; n < NT; n++) {
+                    const float p0 = exp2f(sc[n][0] - ua), p1 = exp2f(sc[n][1] - ua);
+                    const float p2 = exp2f(sc[n][2] - ub), p3 = exp2f(sc[n][3] - ub);
+                    sa += p0 + p1;
+                    sb += p2 + p3;
+                    pf[n][0] = pack_bf16(p0, p1);
+                    pf[n][1] = pack_bf16(p2, p3);
+                }
+                l_a = l_a * fa + sa;
+                l_b = l_b * fb + sb;
+#pragma unroll
+                for (int d = 0; d < DT; d++) {
+                    o[d][0] *= fa;
+                    o[d][1] *= fa;
+                    o[d][2] *= fb;
+                    o[d][3] *= fb;
+                }
+#pragma unroll
+                for (int k2 = 0; k2 < NT / 2; k2++) {
+                    const uint32_t a[4] = {pf[2 * k2][0], pf[2 * k2][1], pf[2 * k2 + 1][0], pf[2 * k2 + 1][1]};
+                    const int vrow = kw0 + k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                    for (int d2 = 0; d2 < DT / 2; d2++) {
+                        uint32_t r0, r1, r2, r3;
+                        ldsm_x4_t(vt + tile_off(vrow, d2 * 2 + (lane >> 4)), r0, r1, r2, r3);
+                        mma_bf16(o[2 * d2], a, r0, r1);
+                        mma_bf16(o[2 * d2 + 1], a, r2, r3);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + s * 8);
+        }
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        if (!DEC) {
+            // every row is whole in its warp: normalise and write
+            const float ia = l_a > 0.0f ? 1.0f / l_a : 0.0f, ib = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+            if (ra < n_rows) {
+                bf16* dst = out + (size_t)(qs0 + ra / G) * ldo + (size_t)(hk * G + ra % G) * HD + (lane & 3) * 2;
+#pragma unroll
+                for (int d = 0; d < DT; d++) *(uint32_t*)(dst + d * 8) = pack_bf16(o[d][0] * ia, o[d][1] * ia);
+            }
+            if (rb < n_rows) {
+                bf16* dst = out + (size_t)(qs0 + rb / G) * ldo + (size_t)(hk * G + rb % G) * HD + (lane & 3) * 2;
+#pragma unroll
+                for (int d = 0; d < DT; d++) *(uint32_t*)(dst + d * 8) = pack_bf16(o[d][2] * ib, o[d][3] * ib);
+            }
+        }
+    }
+    if (!DEC) return;
+
+    // ---------------------------------------------------------------- decode: merge the four warps, then write
+    __syncthreads();                                   // every stage has been consumed: the ring is free
+    float* mo = (float*)smem;                          // [4][16][HD]
+    float* mml = mo + 4 * 16 * HD;                     // [4][16][2]
+    if (warp < 4) {
+        const int r = lane >> 2;
+#pragma unroll
+        for (int d = 0; d < DT; d++) {
+            const int c = d * 8 + (lane & 3) * 2;
+            *(float2*)(mo + (warp * 16 + r) * HD + c) = make_float2(o[d][0], o[d][1]);
+            *(float2*)(mo + (warp * 16 + r + 8) * HD + c) = make_float2(o[d][2], o[d][3]);
+        }
+        if ((lane & 3) == 0) {
+            mml[(warp * 16 + r) * 2] = m_a;
+            mml[(warp * 16 + r) * 2 + 1] = l_a;
+            mml[(warp * 16 + r + 8) * 2] = m_b;
+            mml[(warp * 16 + r + 8) * 2 + 1] = l_b;
+        }
+    }
+    __syncthreads();
+    const int n_splits = gridDim.x, split = blockIdx.x;
+    for (int e = threadIdx.x; e < G * HD; e += AT_THREADS) {
+        const int r = e / HD, d = e % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+        const float U = M == -INFINITY ? 0.0f : M;
+        float ov = 0.0f, lv = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float f = exp2f(mml[(w * 16 + r) * 2] - U);
+            ov = fmaf(f, mo[(w * 16 + r) * HD + d], ov);
+            lv = fmaf(f, mml[(w * 16 + r) * 2 + 1], lv);
+        }
+        const int h = hk * G + r;
+        if (n_splits == 1) {
+            out[(size_t)qs0 * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(lv > 0.0f ? ov / lv : 0.0f);
+        } else {
+            const size_t pi = ((size_t)b * nh + h) * n_splits + split;
+            part_o[pi * HD + d] = ov;
+            if (d == 0) {
+                part_ml[pi * 2] = M;
+                part_ml[pi * 2 + 1] = lv;
+            }
+        }
+    }
+}
+
+// merge the position splits of a decode step in split order: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s
+// (kindi/nbq.cu:635-649)
+__global__ void k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
+                             bf16* __restrict__ out, int ldo, const int* __restrict__ q_start, int nh, int HD) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const size_t base = ((size_t)b * nh + h) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, part_ml[(base + s) * 2]);
+    const float U = M == -INFINITY ? 0.0f : M;
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float l = 0.0f, o = 0.0f;
+        for (int s = 0; s < n_splits; s++) {
+            const float f = exp2f(part_ml[(base + s) * 2] - U);
+            l = fmaf(f, part_ml[(base + s) * 2 + 1], l);
+            o = fmaf(f, part_o[(base + s) * HD + d], o);
+        }
+        out[(size_t)q_start[b] * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+    }
+}
+
+template <int HD, bool DEC>
+static int attn_smem_bytes() {
+    const int stages = DEC ? 3 : 2;
+    int ring = stages * 2 * 64 * HD * 2;
+    int tail = 2 * stages * 8 + 16 + (DEC ? 1 : 4) * 16 * (HD + 8) * 2;
+    int merge = DEC ? (4 * 16 * HD * 4 + 4 * 16 * 2 * 4) : 0;
+    int body = ring + tail;
+    return (body > merge ? body : merge) + 1024;
+}
+
+template <int HD, bool DEC>
+static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, float* part_o,
+                       float* part_ml, const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv,
+                       float scale, int window, const int* table, int table_stride, int n_pages, int grid_x,
+                       int* status, cudaStream_t st) {
+    auto kern = k_attn_mma<HD, DEC>;
+    const int sm = attn_smem_bytes<HD, DEC>();
+    static bool done = false;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    dim3 grid(grid_x, nkv, B);
+    kern<<<grid, AT_THREADS, sm, st>>>(map, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, slot, q_start,
+                                       kv_len, nh, nkv, nh / nkv, scale * 1.4426950408889634f, window, table,
+                                       table_stride, n_pages, status);
+    return (int)cudaGetLastError();
+}
+
+// decode != 0: every sequence brings one token; grid_x = number of position splits (part_o [B][nh][splits][hd] and
+// part_ml [B][nh][splits][2] are scratch when splits > 1). decode == 0: grid_x = ceil(max rows of a sequence / 64)
+// with rows = tokens * (nh / nkv).
+extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* part_o, float* part_ml,
+                           const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv, int hd,
+                           float scale, int window, void* pool, const int* table, int table_stride, int n_pages,
+                           int decode, int grid_x, int* status, cudaStream_t st) {
+    if (B <= 0 || grid_x <= 0) return 0;
+    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+    if (decode && nh / nkv > 16) return (int)cudaErrorInvalidValue;
+    if ((ldq % 8) || (ldo % 2) || ((uintptr_t)q & 15)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map;
+    int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
+    if (rc) return rc;
+#define AT_GO(HD, DEC)                                                                                          \
+    rc = launch_attn<HD, DEC>(map, q, ldq, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv, scale, \
+                              window, table, table_stride, n_pages, grid_x, status, st)
+    if (hd == 128) {
+        if (decode) AT_GO(128, true); else AT_GO(128, false);
+    } else {
+        if (decode) AT_GO(64, true); else AT_GO(64, false);
+    }
+#undef AT_GO
+    if (rc) return rc;
+    if (decode && grid_x > 1) {
+        dim3 grid(nh, B);
+        k_attn_merge<<<grid, hd, 0, st>>>(part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd);
+        return (int)cudaGetLastError();
+    }
+    return 0;
+}

@@ -37,7 +37,7 @@ class EngineError(RuntimeError):
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, ctx: int = 24576, dtype: str = "bfloat16",
                  max_batch: int = 64, device: str = "cuda:0", spec: Optional[ModelSpec] = None,
-                 tensors: Optional[Mapping[str, torch.Tensor]] = None, log=None):
+                 tensors: Optional[Mapping[str, torch.Tensor]] = None, cuda_graphs: bool = True, log=None):
         """``model_dir``: a folder with config.json and safetensors files; or give ``spec`` and ``tensors``
         directly. ``ctx``: the most tokens all live sequences hold together (rounded up per sequence to the cache
         page); it sizes the cache, like the reference's ``ctx`` (``kindi/nanbeige.py:245``)."""
@@ -71,6 +71,10 @@ class Engine:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
+        self.cuda_graphs = bool(cuda_graphs)
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.graph_replays = 0
+        self._graph_warm = set()
 
     # ------------------------------------------------------------------ slots
     def alloc(self) -> int:
@@ -100,19 +104,40 @@ class Engine:
         except CacheFull as ex:
             raise CacheFull("%s while storing %d new tokens; the cache holds %d tokens (ctx = %d)"
                             % (ex, ps.T, cache.tokens_held(), self.ctx)) from None
-        ctx = self._context(ps)
         cache.flush()
-        rows = ctx_rows = None
-        if ps.R:
-            a, n = ps.off["rows"]
-            rows = self._meta_dev[a:a + n]
-        logits = self.model.forward(ctx, rows)
+        graph = None
+        if ps.decode and self.cuda_graphs and ps.R == ps.B and all(e.want == (0,) for e in entries):
+            # the steady decode shape: one token and one wanted row per sequence. The launch sequence is recorded
+            # once per batch size and replayed (the reference records one graph per token too,
+            # kindi/nanbeige.py:728-734); lengths, slots and tokens are read from device memory by the kernels
+            graph = self._graphs.get(ps.B)
+            if graph is None and ps.B in self._graph_warm:
+                graph = self._graphs[ps.B] = _DecodeGraph(self, ps)
+            self._graph_warm.add(ps.B)
+        if graph is not None:
+            logits = graph.replay(ps)
+            self.graph_replays += 1
+        else:
+            ctx = self._context(ps)
+            rows = None
+            if ps.R:
+                a, n = ps.off["rows"]
+                rows = self._meta_dev[a:a + n]
+            logits = self.model.forward(ctx, rows)
         for e, new_len in zip(entries, ps.h_kv_len):
             cache.commit(e.slot, new_len)
         self.steps_run += 1
         return logits
 
-    def _context(self, ps: PackedStep) -> StepContext:
+    def _context(self, ps: PackedStep, dev: Optional[torch.Tensor] = None) -> StepContext:
+        if dev is not None:
+            def seg0(name):
+                a, m = ps.off[name]
+                return dev[a:a + m]
+            return StepContext(T=ps.T, B=ps.B, tok=seg0("tok"), pos=seg0("pos"), seq=seg0("seq"), slot=seg0("slot"),
+                               q_start=seg0("q_start"), kv_len=seg0("kv_len"), h_slot=None, h_q_start=None,
+                               h_kv_len=None, decode=True, max_q=1, max_kv=0, dtype=self.dtype, device=self.device,
+                               status=self.status, cache=self.cache, fast=self.dtype == torch.bfloat16, graph=True)
         n = ps.meta.size
         cap = 1 << max(6, (n - 1).bit_length())
         pin = self._pinned.get(cap)
@@ -190,6 +215,39 @@ class Engine:
 def _to_run_dtype(t: torch.Tensor, run_dtype: str) -> torch.Tensor:
     from ..weights.loader import target_dtype
     return t.to(target_dtype(t.dtype, run_dtype))
+
+
+class _DecodeGraph:
+    """the recorded launch sequence of one decode step for a batch of B sequences, over fixed device buffers"""
+
+    def __init__(self, engine: Engine, ps: PackedStep):
+        self.engine = engine
+        n = ps.meta.size
+        self.pin = torch.empty(n, dtype=torch.int32, pin_memory=True)
+        self.meta = torch.zeros(n, dtype=torch.int32, device=engine.device)
+        self.meta.copy_(torch.from_numpy(ps.meta))
+        self.copied = None
+        ctx = engine._context(ps, self.meta)
+        a, m = ps.off["rows"]
+        rows = self.meta[a:a + m]
+        self.graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        n0 = K.launch_count()
+        with torch.cuda.graph(self.graph):
+            self.logits = engine.model.forward(ctx, rows)
+        self.launches = K.launch_count() - n0        # recorded, not run
+        K.add_launches(-self.launches)
+
+    def replay(self, ps: PackedStep) -> torch.Tensor:
+        if self.copied is not None:
+            self.copied.synchronize()            # the pinned buffer is free again
+        self.pin.copy_(torch.from_numpy(ps.meta))
+        self.meta.copy_(self.pin, non_blocking=True)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+        self.graph.replay()
+        K.add_launches(self.launches)
+        return self.logits
 
 
 class EngineStepper:

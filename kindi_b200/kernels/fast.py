@@ -65,7 +65,21 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
 
 
 def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages) -> bool:
-    return False
+    """the tensor-core attention kernel, where it takes the shape: head size 64 or 128, bf16, aligned rows"""
+    if hd not in (64, 128) or q.dtype != torch.bfloat16 or q.stride(0) % 8 or q.data_ptr() % 16:
+        return False
+    g = nh // nkv
+    if ctx.decode and g <= 16:
+        # position splits: about three CTAs per SM over all (sequence, key/value head) pairs
+        splits = max(1, min(64, -(-3 * N_SM // (ctx.B * nkv))))
+        K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table,
+                   n_pages, decode=True, grid_x=splits, status=ctx.status)
+        return True
+    if ctx.graph:
+        return False
+    K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,
+               decode=False, grid_x=-(-ctx.max_q * g // 64), status=ctx.status)
+    return True
 
 
 def gate_up_swiglu(y, ffn):

@@ -42,6 +42,8 @@ _SIGS = {
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_longlong, c_void_p, c_void_p],
     "kb_gemm_tc_splits": [c_int, c_int],
+    "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                    c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_sample": [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
                   c_void_p],
     "kb_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_float, c_void_p],
@@ -71,7 +73,22 @@ def library_file() -> str:
     return load()._path
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """kernels of this library launched so far (replays of a recorded step count the launches they hold)"""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(rc: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if rc != 0:
         raise KernelError("kindi_b200: launching %s failed with CUDA error %d (%s)"
                           % (what, rc, _err_name(rc)))
@@ -209,3 +226,23 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, 
 
 def gemm_tc_splits(K: int, wanted: int) -> int:
     return load().kb_gemm_tc_splits(K, wanted)
+
+
+def attn_mma(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
+             scale: float, window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, decode: bool,
+             grid_x: int, status: torch.Tensor) -> None:
+    """tensor-core attention over the cache (bf16, head size 64 or 128). decode: one row per sequence, grid_x =
+    position splits; else grid_x = ceil(most rows of a sequence * (nh / nkv) / 64)"""
+    _need_cuda(q, out, pool, table)
+    assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert pool.is_contiguous()
+    part_o = part_ml = None
+    if decode and grid_x > 1:
+        part_o = torch.empty((B, nh, grid_x, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((B, nh, grid_x, 2), dtype=torch.float32, device=q.device)
+    _check(load().kb_attn_mma(_p(q), q.stride(0), _p(out), out.stride(0), _p(part_o), _p(part_ml), _p(slot),
+                              _p(q_start), _p(kv_len), B, nh, nkv, hd, float(scale), int(window), _p(pool), _p(table),
+                              table.stride(0), n_pages, 1 if decode else 0, grid_x, _p(status), _stream()),
+           "attn_mma")
+    if decode and grid_x > 1:
+        add_launches(1)         # the merge of the position splits

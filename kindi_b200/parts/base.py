@@ -67,6 +67,8 @@ class StepContext:
     cache: Any = None                  # the engine's cache (kindi_b200.cache.SequenceCache)
     entry: Any = None                  # the schedule entry being run
     fast: bool = True                  # bfloat16 serving kernels (False: the true 32-bit path)
+    graph: bool = False                # the launches are being recorded for replay: host-side numbers (h_*,
+                                       # max_kv) are not available and nothing may depend on them
 
 
 @dataclass

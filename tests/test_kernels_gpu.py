@@ -67,3 +67,118 @@ def test_gemm_tc(K, M, N, K_, swap, bn, splits):
         K.gemm_tc(a, w, o16, swap=swap, bn=bn, splits=1, status=st)
         assert int(st.item()) == 0
         assert _rel(o16.float(), ref) < 5e-3
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def _make_cache(lengths, nkv, hd, dtype, seed, n_extra_pages=3):
+    """a page pool with random keys and values for sequences of the given lengths, pages handed out in a shuffled
+    order; returns pool [n_pages, 2, nkv, 64, hd], table, and the dense K, V of each sequence"""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    need = [(n + 63) // 64 for n in lengths]
+    n_pages = sum(need) + n_extra_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    pool = (torch.randn(n_pages, 2, nkv, 64, hd, generator=g) * 3.0).to(dtype)       # unmapped space is NOT zero
+    table = torch.full((len(lengths) + 2, n_pages), -1, dtype=torch.int32)
+    dense = []
+    slots = list(range(len(lengths), 0, -1))                # slots in another order than the batch
+    for b, n in enumerate(lengths):
+        k = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        for j in range(need[b]):
+            pg = perm.pop()
+            table[slots[b], j] = pg
+            lo, hi = j * 64, min(n, j * 64 + 64)
+            pool[pg, 0, :, : hi - lo] = k[lo:hi].transpose(0, 1)
+            pool[pg, 1, :, : hi - lo] = v[lo:hi].transpose(0, 1)
+        dense.append((k, v))
+    return pool.cuda(), table.cuda(), dense, torch.tensor(slots, dtype=torch.int32).cuda(), n_pages
+
+
+def _attn_ref(q, k, v, pos, scale, window):
+    """q [nq, nh, hd] rows at positions pos (list); k, v [n, nkv, hd]; float64"""
+    nq, nh, hd = q.shape
+    G = nh // k.shape[1]
+    out = torch.zeros(nq, nh, hd, dtype=torch.float64)
+    for i, p in enumerate(pos):
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(nh):
+            s = (k[lo:p + 1, h // G].double() @ q[i, h].double()) * scale
+            w = torch.softmax(s, dim=0)
+            out[i, h] = w @ v[lo:p + 1, h // G].double()
+    return out
+
+
+def _run_attention(K, kind, dtype, nh, nkv, hd, q_lens, kv_lens, window, seed, boost=None):
+    """kind: 'generic' | 'prefill' | 'decode'. Sequence b brings q_lens[b] rows that end at position kv_lens[b] - 1."""
+    pool, table, dense, slots, n_pages = _make_cache(kv_lens, nkv, hd, dtype, seed)
+    g = torch.Generator(device="cpu").manual_seed(seed + 1)
+    T = sum(q_lens)
+    q = torch.randn(T, nh, hd, generator=g).to(dtype)
+    if boost is not None:
+        # make one far key stand out for one row: scale that key and the row's query along the key's direction
+        b, row, key = boost
+        r0 = sum(q_lens[:b]) + row
+        kvec = dense[b][0][key, 0].float()
+        q[r0, 0] = (kvec / kvec.norm() * 12.0).to(dtype)
+        page = int(table[slots[b], key // 64])
+        pool[page, 0, 0, key % 64] = (kvec / kvec.norm() * 12.0).to(dtype).cuda()
+        dense[b][0][key, 0] = (kvec / kvec.norm() * 12.0).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    pos, seq, q_start = [], [], [0]
+    for b, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        pos += list(range(kl - ql, kl))
+        seq += [b] * ql
+        q_start.append(q_start[-1] + ql)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()      # noqa: E731
+    qd = q.reshape(T, nh * hd).cuda()
+    out = torch.full((T, nh * hd), float("nan"), dtype=dtype).cuda()
+    st = _status()
+    if kind == "generic":
+        K.attn_generic(qd, out, dev(pos), dev(seq), slots, nh, nkv, hd, scale, window, pool, table, n_pages, st)
+    else:
+        G = nh // nkv
+        gx = 5 if kind == "decode" else -(-max(q_lens) * G // 64)
+        K.attn_mma(qd, out, slots, dev(q_start), dev(kv_lens), len(q_lens), nh, nkv, hd, scale, window, pool, table,
+                   n_pages, decode=kind == "decode", grid_x=gx, status=st)
+    assert int(st.item()) == 0
+    got = out.float().cpu().reshape(T, nh, hd)
+    at = 0
+    worst = 0.0
+    for b, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        ref = _attn_ref(q[at:at + ql].float(), dense[b][0].float(), dense[b][1].float(), pos[at:at + ql], scale, window)
+        worst = max(worst, float((got[at:at + ql].double() - ref).abs().max() / ref.abs().max()))
+        at += ql
+    return worst
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (3, 1, 48, 0), (6, 2, 80, 37), (2, 2, 256, 0)])
+def test_attention_generic(K, dtype, tol, nh, nkv, hd, window):
+    err = _run_attention(K, "generic", dtype, nh, nkv, hd, [5, 1, 70, 33], [5, 130, 70, 97], window, seed=hd)
+    assert err < tol
+    err = _run_attention(K, "generic", dtype, nh, nkv, hd, [1, 1], [300, 65], window, seed=hd + 1, boost=(0, 0, 3))
+    assert err < tol
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(20, 4, 128, 0), (3, 1, 64, 0), (8, 8, 128, 0), (6, 2, 64, 100),
+                                              (10, 2, 128, 64), (16, 1, 128, 0)])
+def test_attention_mma_prefill(K, nh, nkv, hd, window):
+    # whole prompts, a chunk that continues an earlier part, single rows, lengths at and around page edges
+    err = _run_attention(K, "prefill", torch.bfloat16, nh, nkv, hd, [64, 1, 130, 33, 7], [64, 129, 130, 97, 200],
+                         window, seed=nh)
+    assert err < 1e-2
+    # one far key among hundreds decides a row
+    err = _run_attention(K, "prefill", torch.bfloat16, nh, nkv, hd, [40, 3], [700, 65], window=0, seed=nh + 1,
+                         boost=(0, 39, 5))
+    assert err < 1e-2
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(20, 4, 128, 0), (3, 1, 64, 0), (8, 8, 128, 0), (14, 2, 64, 100),
+                                              (10, 2, 128, 64), (16, 1, 128, 0)])
+def test_attention_mma_decode(K, nh, nkv, hd, window):
+    err = _run_attention(K, "decode", torch.bfloat16, nh, nkv, hd, [1] * 6, [1, 64, 65, 700, 129, 320], window,
+                         seed=nh + 7)
+    assert err < 1e-2
+    err = _run_attention(K, "decode", torch.bfloat16, nh, nkv, hd, [1, 1], [900, 65], window=0, seed=nh + 9,
+                         boost=(0, 0, 3))
+    assert err < 1e-2
