@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 # max |engine - plain| / max |plain| over a request's logits. 32-bit: sums of a few hundred terms in another order
 # than the float64 reference. bfloat16: activations and cached keys/values are rounded to 8 bits of mantissa between
 # the operations (2^-9 relative each), a handful of roundings per layer.
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
 LENGTHS = [5, 9, 13, 1, 70, 130, 33, 64, 97]
 
 
@@ -31,7 +31,7 @@ def _plain_logits(model_dir, reqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_replay_modes_match_plain(models, tmp_path, name, dtype):
     from kindi_b200.engine.engine import Engine
     # the float32 run reads the folder stored in float32, the bfloat16 run the one stored in bfloat16
@@ -50,12 +50,15 @@ def test_replay_modes_match_plain(models, tmp_path, name, dtype):
         assert eng.cache.slots.n_held == 0 and all(g.pages.pool.n_held == 0 for g in eng.cache.groups)
         results[mode] = tiny.collect(out, steps, vocab)
         del eng
+    worst = 0.0
     for mode, got in results.items():
         assert len(got) == sum(len(t) for t in reqs.values()), mode
         for rid, toks in reqs.items():
             mine = np.stack([got[(rid, i)] for i in range(len(toks))])
             err = tiny.rel_err(mine, want[rid])
+            worst = max(worst, err)
             assert err <= TOL[dtype], "%s %s %s: %.3g" % (mode, rid, dtype, err)
+    print("worst relative error %s %s: %.3g" % (name, dtype, worst))
     if dtype == "float32":
         # the 32-bit path sums in an order that depends on positions only: the three ways of cutting agree bit for bit
         for key, row in results["whole"].items():

@@ -21,7 +21,16 @@ TINY_C = dict(architectures=["NanbeigeForCausalLM"], model_type="llama", vocab_s
               intermediate_size=200, num_hidden_layers=4, num_attention_heads=6, num_key_value_heads=2, head_dim=48,
               rms_norm_eps=3e-6, rope_theta=1000000.0, tie_word_embeddings=False, sliding_window=40,
               layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"])
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# D and E have the head sizes the tensor-core attention kernels take (64, 128) with 5 and 3 query heads per key/value
+# head, so the bfloat16 runs of these two go through the serving kernels end to end
+TINY_D = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=500, hidden_size=160,
+              intermediate_size=264, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=1, head_dim=64,
+              rms_norm_eps=1e-5, rope_theta=70000000.0, tie_word_embeddings=False)
+TINY_E = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=777, hidden_size=200,
+              intermediate_size=344, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
+              rms_norm_eps=2e-6, rope_theta=250000.0, tie_word_embeddings=True, sliding_window=70,
+              layer_types=["full_attention", "sliding_attention", "full_attention"])
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
 def make_model(tmp_path, name: str, dtype: str = "bfloat16") -> str:
