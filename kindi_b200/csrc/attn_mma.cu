@@ -309,17 +309,31 @@ __global__ void __launch_bounds__(AT_THREADS) k_attn_mma(const __grid_constant__
 // (kindi/nbq.cu:635-649)
 __global__ void k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
                              bf16* __restrict__ out, int ldo, const int* __restrict__ q_start, int nh, int HD) {
+    __shared__ float sf[64], sl[64];              // at most 64 splits: each split's weight 2^(m_s - M), and its sum
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nh + h) * n_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; s++) M = fmaxf(M, part_ml[(base + s) * 2]);
-    const float U = M == -INFINITY ? 0.0f : M;
+    if (threadIdx.x < 32) {
+        float m0 = threadIdx.x < n_splits ? part_ml[(base + threadIdx.x) * 2] : -INFINITY;
+        float m1 = threadIdx.x + 32 < n_splits ? part_ml[(base + threadIdx.x + 32) * 2] : -INFINITY;
+        const float M = kb_warp_max(fmaxf(m0, m1));
+        const float U = M == -INFINITY ? 0.0f : M;
+        sf[threadIdx.x] = exp2f(m0 - U);
+        sf[threadIdx.x + 32] = exp2f(m1 - U);
+        sl[threadIdx.x] = threadIdx.x < n_splits ? part_ml[(base + threadIdx.x) * 2 + 1] : 0.0f;
+        sl[threadIdx.x + 32] = threadIdx.x + 32 < n_splits ? part_ml[(base + threadIdx.x + 32) * 2 + 1] : 0.0f;
+    }
+    __syncthreads();
+    float l = 0.0f;
+    for (int s = 0; s < n_splits; s++) l = fmaf(sf[s], sl[s], l);
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float l = 0.0f, o = 0.0f;
-        for (int s = 0; s < n_splits; s++) {
-            const float f = exp2f(part_ml[(base + s) * 2] - U);
-            l = fmaf(f, part_ml[(base + s) * 2 + 1], l);
-            o = fmaf(f, part_o[(base + s) * HD + d], o);
+        float o = 0.0f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) t[j] = (s0 + j < n_splits) ? part_o[(base + s0 + j) * HD + d] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (s0 + j < n_splits) o = fmaf(sf[s0 + j], t[j], o);
         }
         out[(size_t)q_start[b] * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
     }
@@ -363,6 +377,7 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
                            float scale, int window, void* pool, const int* table, int table_stride, int n_pages,
                            int decode, int grid_x, int* status, cudaStream_t st) {
     if (B <= 0 || grid_x <= 0) return 0;
+    if (decode && grid_x > 64) return (int)cudaErrorInvalidValue;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
     if (decode && nh / nkv > 16) return (int)cudaErrorInvalidValue;
     if ((ldq % 8) || (ldo % 2) || ((uintptr_t)q & 15)) return (int)cudaErrorInvalidValue;

@@ -1,15 +1,16 @@
 // bfloat16 matrix products on the 5th-generation tensor cores: C = A W^T with both operands K-major.
 //
-// One CTA computes a 128 x BN tile of D = P Q^T, where P ("the 128-row side") and Q ("the BN-row side") are
-// [rows][K] bf16 tensors read by TMA (boxes of 64 K-elements, 128-byte swizzle, zero fill past the edges, no
-// multicast) into a ring of shared-memory stages; one elected thread issues tcgen05.mma (M 128, N BN, K 16, fp32
-// accumulator in tensor memory); tcgen05.commit frees a stage when its MMAs are done; four epilogue warps read the
-// accumulator with tcgen05.ld and write C.
+// A work unit is a 128 x BN tile of D = P Q^T over one range of K, where P ("the 128-row side") and Q ("the BN-row
+// side") are [rows][K] bf16 tensors read by TMA (boxes of 64 K-elements, 128-byte swizzle, zero fill past the edges,
+// no multicast) into a ring of shared-memory stages. CTAs are persistent: CTA c takes units c, c + gridDim.x, ...;
+// a producer warp keeps the ring full across unit boundaries, one elected thread issues tcgen05.mma (M 128, N BN,
+// K 16, fp32 accumulator in tensor memory), tcgen05.commit frees a stage when its MMAs are done, and four epilogue
+// warps drain one of TWO accumulators with tcgen05.ld while the MMAs of the next unit fill the other.
 //   - prefill form: P = activations (tokens), Q = weights (features): a TMEM lane is a token, a column a feature.
 //   - decode form ("swap"): P = weights (128 features a tile), Q = the few activation rows (BN = 16..128 tokens):
 //     the weights stream through the 128-row side at memory speed and the batch is the narrow side.
-// gridDim.z splits K; each split writes its own fp32 partial plane (no atomics: the caller adds the planes in
-// order, so results are the same on every run).
+// K may be split: each split writes its own fp32 plane (no atomics: the consumer adds the planes in order, so
+// results are the same on every run).
 // The reference's counterparts are its int8 mma.sync prompt product (kindi/nbq_mm.cu:23-178) and its dp4a
 // matrix-vector products (kindi/nbq.cu:266-296).
 #include "sm100.cuh"
@@ -24,33 +25,37 @@ struct TcSmem {
     static constexpr int B_BYTES = BN * TC_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;     // + alignment slack
+    static constexpr int N_BARS = 2 * STAGES + 4;
+    static constexpr int TOTAL = BAR_OFF + N_BARS * 8 + 16 + 1024;     // + alignment slack
 };
 
 template <int BN, int STAGES, bool SWAP, typename TC>
 __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ CUtensorMap mapP,
         const __grid_constant__ CUtensorMap mapQ, TC* __restrict__ C, int rowsP, int rowsQ, int K, int ldc,
-        long long split_stride, int kb_per_split, int* status) {
+        long long split_stride, int kb_per_split, int n_splits, int* status) {
     using S = TcSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bar_full = sbase + S::BAR_OFF, bar_empty = bar_full + STAGES * 8, bar_acc = bar_empty + STAGES * 8;
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + S::BAR_OFF + (2 * STAGES + 1) * 8);
+    const uint32_t bar_full = sbase + S::BAR_OFF, bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_acc_full = bar_empty + STAGES * 8, bar_acc_empty = bar_acc_full + 16;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + S::BAR_OFF + S::N_BARS * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int p0 = blockIdx.x * TC_BM, q0 = blockIdx.y * BN;
+    const int tilesP = (rowsP + TC_BM - 1) / TC_BM, tilesQ = (rowsQ + BN - 1) / BN;
+    const int n_units = tilesP * tilesQ * n_splits;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
-    const int kb0 = blockIdx.z * kb_per_split;
-    const int kb1 = min(total_kb, kb0 + kb_per_split);
-    const int nkb = kb1 - kb0;                      // > 0 by construction of the grid
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;          // columns of one accumulator
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + s * 8, 1);
             mbar_init(bar_empty + s * 8, 1);
         }
-        mbar_init(bar_acc, 1);
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_acc_full + a * 8, 1);
+            mbar_init(bar_acc_empty + a * 8, 4);
+        }
         mbar_fence_init();
         tma_prefetch_desc(&mapP);
         tma_prefetch_desc(&mapQ);
@@ -66,47 +71,67 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; i++) {
-                const int s = i % STAGES;
-                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-                if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, status)) break;
-                mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
-                const uint32_t dst = sbase + s * S::STAGE_BYTES;
-                tma_load_2d(dst, &mapP, (kb0 + i) * TC_BK, p0, bar_full + s * 8);
-                tma_load_2d(dst + S::A_BYTES, &mapQ, (kb0 + i) * TC_BK, q0, bar_full + s * 8);
+            uint32_t n = 0;                                  // k-blocks loaded so far (ring position)
+            bool ok = true;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const int tp = u % tilesP, rest = u / tilesP, tq = rest % tilesQ, sp = rest / tilesQ;
+                const int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
+                for (int kb = kb0; kb < kb1; kb++, n++) {
+                    const int s = n % STAGES;
+                    const uint32_t ph = (n / STAGES) & 1u;
+                    if (!(ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, status))) break;
+                    mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
+                    const uint32_t dst = sbase + s * S::STAGE_BYTES;
+                    tma_load_2d(dst, &mapP, kb * TC_BK, tp * TC_BM, bar_full + s * 8);
+                    tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+            uint32_t n = 0, it = 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % STAGES;
-                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-                ok = mbar_wait(bar_full + s * 8, ph, status);
-                if (!ok) break;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, it++) {
+                const int sp = (u / tilesP) / tilesQ;
+                const int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
+                const uint32_t acc = it & 1u;
+                if (!(ok = mbar_wait(bar_acc_empty + acc * 8, ((it >> 1) & 1u) ^ 1u, status))) break;
                 tc_fence_after();
-                const uint32_t a = sbase + s * S::STAGE_BYTES, b = a + S::A_BYTES;
+                const uint32_t d = tmem + acc * ACC_COLS;
+                for (int kb = kb0; kb < kb1; kb++, n++) {
+                    const int s = n % STAGES;
+                    const uint32_t ph = (n / STAGES) & 1u;
+                    if (!(ok = mbar_wait(bar_full + s * 8, ph, status))) break;
+                    tc_fence_after();
+                    const uint32_t a = sbase + s * S::STAGE_BYTES, b = a + S::A_BYTES;
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++)
-                    umma_bf16(tmem, umma_desc_sw128(a + k * 32), umma_desc_sw128(b + k * 32), idesc,
-                              (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(bar_empty + s * 8);
+                    for (int k = 0; k < TC_BK / 16; k++)
+                        umma_bf16(d, umma_desc_sw128(a + k * 32), umma_desc_sw128(b + k * 32), idesc,
+                                  (kb > kb0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar_empty + s * 8);
+                }
+                umma_commit(bar_acc_full + acc * 8);
             }
-            umma_commit(bar_acc);
         }
     } else {
         // epilogue warps 2..5 own TMEM lanes 32 * (warp % 4) .. + 31
         const int quarter = warp & 3;
-        const bool ok = mbar_wait(bar_acc, 0, status);
-        tc_fence_after();
-        const int prow = p0 + quarter * 32 + lane;           // row of the 128-row side this thread holds
-        TC* Cz = C + (size_t)blockIdx.z * split_stride;
-        if (ok) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, it++) {
+            const int tp = u % tilesP, rest = u / tilesP, tq = rest % tilesQ, sp = rest / tilesQ;
+            const int p0 = tp * TC_BM, q0 = tq * BN;
+            const uint32_t acc = it & 1u;
+            if (!(ok = mbar_wait(bar_acc_full + acc * 8, (it >> 1) & 1u, status))) break;
+            tc_fence_after();
+            const int prow = p0 + quarter * 32 + lane;           // row of the 128-row side this thread holds
+            TC* Cz = C + (size_t)sp * split_stride;
+            const uint32_t tbase = tmem + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
-                tmem_ld_32x16(tmem + ((uint32_t)(quarter * 32) << 16) + c0, r);
+                tmem_ld_32x16(tbase + c0, r);
                 tmem_ld_wait();
                 if (SWAP) {
                     // C[token q0 + c][feature prow]: a warp's 32 lanes write 32 consecutive features
@@ -144,6 +169,10 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                     }
                 }
             }
+            // this warp has read its lanes of the accumulator: hand it back to the MMA thread
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + acc * 8);
         }
     }
     tc_fence_before();
@@ -152,6 +181,16 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
+}
+
+static int kb_sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
 }
 
 template <int BN, int STAGES, bool SWAP, typename TC>
@@ -168,8 +207,9 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     int kbps = (total_kb + splits - 1) / splits;
     int z = (total_kb + kbps - 1) / kbps;               // every split has at least one k-block
-    dim3 grid((rowsP + TC_BM - 1) / TC_BM, (rowsQ + BN - 1) / BN, z);
-    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(mp, mq, (TC*)C, rowsP, rowsQ, K, ldc, split_stride, kbps, status);
+    const int units = ((rowsP + TC_BM - 1) / TC_BM) * ((rowsQ + BN - 1) / BN) * z;
+    const int grid = units < kb_sm_count() ? units : kb_sm_count();
+    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(mp, mq, (TC*)C, rowsP, rowsQ, K, ldc, split_stride, kbps, z, status);
     return (int)cudaGetLastError();
 }
 

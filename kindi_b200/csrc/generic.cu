@@ -41,12 +41,26 @@ extern "C" int kb_embed(const void* table, int wdtype, const int* tok, float* x,
 // row r of the output is row t = rows ? rows[r] : r of the residual. v = x[t] + sum_s delta[s][t] (s in order);
 // written back to x when write_back; y = (rsqrt(mean(v^2) + eps) * v) * w, the two products rounded one after the
 // other as the reference does (kindi/nbq.cu:428-430).
+// The planes are read with independent loads (eight in flight per element) and then added in order, so the sum is
+// the same as a plain loop's while the few blocks of a decode step are not bound by load latency.
+#define NORM_THREADS 512
+__device__ __forceinline__ float kb_sum_planes(float v, const float* __restrict__ d, int n, size_t stride) {
+    for (int s0 = 0; s0 < n; s0 += 8) {
+        float t[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) t[j] = (s0 + j < n) ? d[(size_t)(s0 + j) * stride] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (s0 + j < n) v += t[j];
+    }
+    return v;
+}
 template <typename TY, typename TW>
-__global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ x, const float* __restrict__ delta,
+__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict__ x, const float* __restrict__ delta,
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, TY* __restrict__ y,
         const int* __restrict__ rows, int T, int E, int write_back, int* status) {
     extern __shared__ float sv[];
-    __shared__ float red[8];
+    __shared__ float red[NORM_THREADS / 32];
     const int r = blockIdx.x;
     int t = rows ? rows[r] : r;
     if (t < 0 || t >= T) {
@@ -54,10 +68,11 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ x, cons
         t = 0;
     }
     float* xr = x + (size_t)t * E;
+    const float* dr = delta + (size_t)t * E;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < E; i += 256) {
+    for (int i = threadIdx.x; i < E; i += NORM_THREADS) {
         float v = xr[i];
-        for (int s = 0; s < n_delta; s++) v += delta[(size_t)s * delta_stride + (size_t)t * E + i];
+        if (n_delta > 0) v = kb_sum_planes(v, dr + i, n_delta, delta_stride);
         if (write_back) xr[i] = v;
         sv[i] = v;
         ss = fmaf(v, v, ss);
@@ -67,10 +82,10 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ x, cons
     __syncthreads();
     float tot = red[0];
 #pragma unroll
-    for (int k = 1; k < 8; k++) tot += red[k];
+    for (int k = 1; k < NORM_THREADS / 32; k++) tot += red[k];
     const float scale = rsqrtf(tot / (float)E + eps);
     TY* yr = y + (size_t)r * E;
-    for (int i = threadIdx.x; i < E; i += 256)
+    for (int i = threadIdx.x; i < E; i += NORM_THREADS)
         yr[i] = kb_from_f<TY>(__fmul_rn(__fmul_rn(scale, sv[i]), kb_to_f<TW>(w[i])));
 }
 
@@ -84,7 +99,7 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
     do {                                                                                                      \
         if (sm > 48 * 1024)                                                                                   \
             cudaFuncSetAttribute(k_add_rmsnorm<TY, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-        k_add_rmsnorm<TY, TW><<<n_out, 256, sm, st>>>(x, delta, n_delta, (size_t)delta_stride, (const TW*)w,  \
+        k_add_rmsnorm<TY, TW><<<n_out, NORM_THREADS, sm, st>>>(x, delta, n_delta, (size_t)delta_stride, (const TW*)w,  \
                                                       eps, (TY*)y, rows, T, E, write_back, status);           \
     } while (0)
     if (ydtype == KB_F32 && wdtype == KB_F32) KB_NORM(float, float);
@@ -199,7 +214,15 @@ __global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t pl
     }
     auto rd = [&](int i) {
         float v = kb_to_f<TIN>(src[i]);
-        for (int s = 1; s < n_planes; s++) v += kb_to_f<TIN>(src[(size_t)s * plane_stride + i]);
+        for (int s0 = 1; s0 < n_planes; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                t[j] = (s0 + j < n_planes) ? kb_to_f<TIN>(src[(size_t)(s0 + j) * plane_stride + i]) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (s0 + j < n_planes) v += t[j];
+        }
         return v;
     };
     const int half = rot / 2;
@@ -340,9 +363,20 @@ __global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_
     const long long t = i / F;
     const int c = (int)(i % F);
     float g = 0.0f, u = 0.0f;
-    for (int s = 0; s < n_planes; s++) {
-        g += kb_to_f<TIN>(gu[(size_t)s * plane_stride + t * 2 * F + c]);
-        u += kb_to_f<TIN>(gu[(size_t)s * plane_stride + t * 2 * F + F + c]);
+    for (int s0 = 0; s0 < n_planes; s0 += 4) {
+        float tg[4], tu[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const bool on = s0 + j < n_planes;
+            tg[j] = on ? kb_to_f<TIN>(gu[(size_t)(s0 + j) * plane_stride + t * 2 * F + c]) : 0.0f;
+            tu[j] = on ? kb_to_f<TIN>(gu[(size_t)(s0 + j) * plane_stride + t * 2 * F + F + c]) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (s0 + j < n_planes) {
+                g += tg[j];
+                u += tu[j];
+            }
     }
     out[i] = kb_from_f<T>(g / (1.0f + expf(-g)) * u);
 }

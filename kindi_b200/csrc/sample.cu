@@ -25,7 +25,16 @@ __device__ __forceinline__ unsigned long long sm_fix(float w) { return (unsigned
 __device__ void sm_argmax(const float* z, int V, float* s_v, int* s_i, float& best, int& best_i) {
     float v = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += SM_THREADS) {
+    // four strided loads in flight per thread; within a thread indices rise, so ">" keeps the lowest index of a tie
+    int i = threadIdx.x;
+    for (; i + 3 * SM_THREADS < V; i += 4 * SM_THREADS) {
+        const float x0 = z[i], x1 = z[i + SM_THREADS], x2 = z[i + 2 * SM_THREADS], x3 = z[i + 3 * SM_THREADS];
+        if (x0 > v || idx == 0x7fffffff) { v = x0; idx = i; }
+        if (x1 > v) { v = x1; idx = i + SM_THREADS; }
+        if (x2 > v) { v = x2; idx = i + 2 * SM_THREADS; }
+        if (x3 > v) { v = x3; idx = i + 3 * SM_THREADS; }
+    }
+    for (; i < V; i += SM_THREADS) {
         float x = z[i];
         if (x > v || idx == 0x7fffffff) { v = x; idx = i; }
     }

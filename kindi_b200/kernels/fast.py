@@ -29,11 +29,20 @@ def wants_planes(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def _splits_for(m: int, n: int, k: int, bn: int) -> int:
-    """enough CTAs to keep every SM streaming weights: about two per SM, each with at least two K blocks"""
+    """how many ways to split K so that the persistent CTAs (one per SM) finish together: the cost of a launch is
+    the number of rounds of units times the K blocks of a unit; more planes cost the consumer more reads"""
     tiles = -(-n // 128) * -(-m // bn)
     total_kb = -(-k // 64)
-    want = max(1, min(total_kb // 2, round(2 * N_SM / tiles)))
-    return want
+    best, best_cost = 1, None
+    for s in range(1, min(16, total_kb) + 1):
+        kbps = -(-total_kb // s)
+        if -(-total_kb // kbps) != s or (s > 1 and kbps < 2):
+            continue
+        rounds = -(-tiles * s // N_SM)
+        cost = rounds * (kbps + 0.5) + 0.05 * s
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
