@@ -212,6 +212,7 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=CONFIG_3B["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     a = ap.parse_args(argv)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -225,6 +226,9 @@ def main(argv=None) -> int:
     import torch
     from kindi_b200.engine.batch import layout
     pk = peaks()
+    if a.no_pdl:
+        from kindi_b200.kernels import lib as _K
+        _K.set_pdl(False)
     max_b = max(a.batch, 1 if a.no_points else 64)
     ctx = max_b * (a.context + a.steps * 2 + a.warmup + 256) + PREFILL_TOKENS + 64
     eng = build_engine(a.layers, ctx, max_b)

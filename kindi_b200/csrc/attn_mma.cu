@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(AT_THREADS) k_attn_mma(const __grid_constant__
     bf16* qs = (bf16*)(smem + AT_STAGES * STAGE_BYTES + 2 * AT_STAGES * 8 + 16);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, hk = blockIdx.y;
+    kb_pdl_launch();
+    kb_pdl_wait();                               // the step's metadata, Q and the newest keys come from earlier kernels
     const int qs0 = q_start[b], qlen = q_start[b + 1] - qs0, kvl = kv_len[b];
     const int pos0 = kvl - qlen;                 // position of the sequence's first row of this step
     const int n_rows = qlen * G;
@@ -309,7 +311,12 @@ __global__ void __launch_bounds__(AT_THREADS) k_attn_mma(const __grid_constant__
 // (kindi/nbq.cu:635-649)
 __global__ void k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
                              bf16* __restrict__ out, int ldo, const int* __restrict__ q_start, int nh, int HD) {
+    // blockDim = 4 * HD: group g = threadIdx.x / HD adds the splits 16 g .. 16 g + 15 for its column, then the four
+    // group sums are added in group order: every sum has a fixed order
     __shared__ float sf[64], sl[64];              // at most 64 splits: each split's weight 2^(m_s - M), and its sum
+    __shared__ float so[4][256];
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nh + h) * n_splits;
     if (threadIdx.x < 32) {
@@ -322,19 +329,21 @@ __global__ void k_attn_merge(const float* __restrict__ part_o, const float* __re
         sl[threadIdx.x] = threadIdx.x < n_splits ? part_ml[(base + threadIdx.x) * 2 + 1] : 0.0f;
         sl[threadIdx.x + 32] = threadIdx.x + 32 < n_splits ? part_ml[(base + threadIdx.x + 32) * 2 + 1] : 0.0f;
     }
+    const int g = threadIdx.x / HD, d = threadIdx.x % HD;
+    float t[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) t[j] = (g * 16 + j < n_splits) ? part_o[(base + g * 16 + j) * HD + d] : 0.0f;
     __syncthreads();
-    float l = 0.0f;
-    for (int s = 0; s < n_splits; s++) l = fmaf(sf[s], sl[s], l);
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float o = 0.0f;
-        for (int s0 = 0; s0 < n_splits; s0 += 8) {
-            float t[8];
+    float o = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; j++) t[j] = (s0 + j < n_splits) ? part_o[(base + s0 + j) * HD + d] : 0.0f;
-#pragma unroll
-            for (int j = 0; j < 8; j++)
-                if (s0 + j < n_splits) o = fmaf(sf[s0 + j], t[j], o);
-        }
+    for (int j = 0; j < 16; j++)
+        if (g * 16 + j < n_splits) o = fmaf(sf[g * 16 + j], t[j], o);
+    so[g][d] = o;
+    __syncthreads();
+    if (g == 0) {
+        float l = 0.0f;
+        for (int s = 0; s < n_splits; s++) l = fmaf(sf[s], sl[s], l);
+        o = ((so[0][d] + so[1][d]) + so[2][d]) + so[3][d];
         out[(size_t)q_start[b] * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
     }
 }
@@ -363,7 +372,7 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
         done = true;
     }
     dim3 grid(grid_x, nkv, B);
-    kern<<<grid, AT_THREADS, sm, st>>>(map, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, slot, q_start,
+    kb_launch(kern, grid, AT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, slot, q_start,
                                        kv_len, nh, nkv, nh / nkv, scale * 1.4426950408889634f, window, table,
                                        table_stride, n_pages, status);
     return (int)cudaGetLastError();
@@ -396,7 +405,7 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
     if (rc) return rc;
     if (decode && grid_x > 1) {
         dim3 grid(nh, B);
-        k_attn_merge<<<grid, hd, 0, st>>>(part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd);
+        kb_launch(k_attn_merge, grid, 4 * hd, 0, st, part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd);
         return (int)cudaGetLastError();
     }
     return 0;

@@ -56,3 +56,33 @@ __device__ __forceinline__ size_t kb_kv_offset(const KbCacheView& c, int page, i
 }
 
 #define KB_LAUNCH_RET() return (int)cudaGetLastError()
+
+// Programmatic dependent launch. Every kernel of the library begins with kb_pdl_launch() (the next kernel of the
+// stream may be scheduled as soon as all CTAs of this one have started) and calls kb_pdl_wait() before its first
+// read of anything an earlier kernel wrote and before its first global write (until then it may only set up
+// barriers and tensor memory and fetch weights, which no kernel writes). The wait returns when the whole preceding
+// kernel has finished and its writes are visible, so results are those of strictly ordered launches; what is
+// gained is that launch latency and prologues overlap the predecessor's tail.
+__device__ __forceinline__ void kb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void kb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int g_kb_pdl;            // 1: launches carry the programmatic-serialization attribute
+
+#ifdef __cplusplus
+#include <utility>
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_kb_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+#endif

@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         long long split_stride, int kb_per_split, int n_splits, int* status) {
     using S = TcSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
+    kb_pdl_launch();
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar_full = sbase + S::BAR_OFF, bar_empty = bar_full + STAGES * 8;
@@ -73,18 +74,43 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         if (lane == 0) {
             uint32_t n = 0;                                  // k-blocks loaded so far (ring position)
             bool ok = true;
+            // In the decode form the 128-row side is the weights, which no kernel writes: their tiles are requested
+            // BEFORE the wait on the preceding kernel, so the ring is already filling while that kernel finishes;
+            // the activation tiles of those stages follow right after the wait.
+            bool waited = !SWAP;
+            int pend_kb[STAGES], pend_tq[STAGES], n_pend = 0;
+            if (!SWAP) kb_pdl_wait();
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 const int tp = u % tilesP, rest = u / tilesP, tq = rest % tilesQ, sp = rest / tilesQ;
                 const int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
                 for (int kb = kb0; kb < kb1; kb++, n++) {
                     const int s = n % STAGES;
                     const uint32_t ph = (n / STAGES) & 1u;
+                    if (!waited && n_pend == STAGES) {
+                        kb_pdl_wait();
+                        waited = true;
+                        for (int j = 0; j < n_pend; j++)
+                            tma_load_2d(sbase + j * S::STAGE_BYTES + S::A_BYTES, &mapQ, pend_kb[j] * TC_BK,
+                                        pend_tq[j] * BN, bar_full + j * 8);
+                    }
                     if (!(ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, status))) break;
                     mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
                     const uint32_t dst = sbase + s * S::STAGE_BYTES;
                     tma_load_2d(dst, &mapP, kb * TC_BK, tp * TC_BM, bar_full + s * 8);
-                    tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
+                    if (waited) {
+                        tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
+                    } else {
+                        pend_kb[n_pend] = kb;                // stage n_pend == s here: the ring has not wrapped yet
+                        pend_tq[n_pend] = tq;
+                        n_pend++;
+                    }
                 }
+            }
+            if (!waited) {
+                kb_pdl_wait();
+                for (int j = 0; j < n_pend; j++)
+                    tma_load_2d(sbase + j * S::STAGE_BYTES + S::A_BYTES, &mapQ, pend_kb[j] * TC_BK, pend_tq[j] * BN,
+                                bar_full + j * 8);
             }
         }
     } else if (warp == 1) {
@@ -119,6 +145,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         const int quarter = warp & 3;
         uint32_t it = 0;
         bool ok = true;
+        kb_pdl_wait();                                   // C may be memory that an earlier kernel still reads
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, it++) {
             const int tp = u % tilesP, rest = u / tilesP, tq = rest % tilesQ, sp = rest / tilesQ;
             const int p0 = tp * TC_BM, q0 = tq * BN;
@@ -209,7 +236,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
     int z = (total_kb + kbps - 1) / kbps;               // every split has at least one k-block
     const int units = ((rowsP + TC_BM - 1) / TC_BM) * ((rowsQ + BN - 1) / BN) * z;
     const int grid = units < kb_sm_count() ? units : kb_sm_count();
-    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(mp, mq, (TC*)C, rowsP, rowsQ, K, ldc, split_stride, kbps, z, status);
+    kb_launch(kern, grid, TC_THREADS, S::TOTAL, st, mp, mq, (TC*)C, rowsP, rowsQ, K, ldc, split_stride, kbps, z, status);
     return (int)cudaGetLastError();
 }
 

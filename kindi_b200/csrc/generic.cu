@@ -12,11 +12,16 @@
 // starts at -1e30 (kindi/nbq.cu:525-633), SwiGLU g / (1 + exp(-g)) * u (kindi/nbq.cu:461-467).
 #include "common.cuh"
 
+int g_kb_pdl = 1;
+extern "C" void kb_set_pdl(int on) { g_kb_pdl = on ? 1 : 0; }
+
 // ------------------------------------------------------------------------------------------------ embedding
 // x[t][:] = table[tok[t]][:] as 32-bit (no scaling: kindi/nbq.cu:472-487)
 template <typename TW>
 __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ tok, float* __restrict__ x, int E,
                         int vocab, int* status) {
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int t = blockIdx.x;
     const int id = tok[t];
     float* xr = x + (size_t)t * E;
@@ -32,8 +37,8 @@ __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ to
 extern "C" int kb_embed(const void* table, int wdtype, const int* tok, float* x, int T, int E, int vocab,
                         int* status, cudaStream_t st) {
     if (T <= 0) return 0;
-    if (wdtype == KB_F32) k_embed<float><<<T, 256, 0, st>>>((const float*)table, tok, x, E, vocab, status);
-    else k_embed<bf16><<<T, 256, 0, st>>>((const bf16*)table, tok, x, E, vocab, status);
+    if (wdtype == KB_F32) kb_launch(k_embed<float>, T, 256, 0, st, (const float*)table, tok, x, E, vocab, status);
+    else kb_launch(k_embed<bf16>, T, 256, 0, st, (const bf16*)table, tok, x, E, vocab, status);
     KB_LAUNCH_RET();
 }
 
@@ -43,7 +48,8 @@ extern "C" int kb_embed(const void* table, int wdtype, const int* tok, float* x,
 // other as the reference does (kindi/nbq.cu:428-430).
 // The planes are read with independent loads (eight in flight per element) and then added in order, so the sum is
 // the same as a plain loop's while the few blocks of a decode step are not bound by load latency.
-#define NORM_THREADS 512
+#define NORM_THREADS 1024
+#define NORM_MAX_E 51200
 __device__ __forceinline__ float kb_sum_planes(float v, const float* __restrict__ d, int n, size_t stride) {
     for (int s0 = 0; s0 < n; s0 += 8) {
         float t[8];
@@ -55,12 +61,34 @@ __device__ __forceinline__ float kb_sum_planes(float v, const float* __restrict_
     }
     return v;
 }
-template <typename TY, typename TW>
+__device__ __forceinline__ float4 kb_sum_planes4(float4 v, const float* __restrict__ d, int n, size_t stride) {
+    for (int s0 = 0; s0 < n; s0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            t[j] = (s0 + j < n) ? *(const float4*)(d + (size_t)(s0 + j) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (s0 + j < n) {
+                v.x += t[j].x;
+                v.y += t[j].y;
+                v.z += t[j].z;
+                v.w += t[j].w;
+            }
+    }
+    return v;
+}
+// VEC: the width is a multiple of 4 and every row is 16-byte aligned: a thread takes four neighbouring elements (one
+// pass for widths up to 4096) with all its loads in flight at once. Each element's own sum (residual, then the
+// planes in order) is the same in both forms.
+template <typename TY, typename TW, bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict__ x, const float* __restrict__ delta,
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, TY* __restrict__ y,
         const int* __restrict__ rows, int T, int E, int write_back, int* status) {
     extern __shared__ float sv[];
     __shared__ float red[NORM_THREADS / 32];
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int r = blockIdx.x;
     int t = rows ? rows[r] : r;
     if (t < 0 || t >= T) {
@@ -70,12 +98,25 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict_
     float* xr = x + (size_t)t * E;
     const float* dr = delta + (size_t)t * E;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < E; i += NORM_THREADS) {
-        float v = xr[i];
-        if (n_delta > 0) v = kb_sum_planes(v, dr + i, n_delta, delta_stride);
-        if (write_back) xr[i] = v;
-        sv[i] = v;
-        ss = fmaf(v, v, ss);
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < E; i += NORM_THREADS * 4) {
+            float4 v = *(const float4*)(xr + i);
+            if (n_delta > 0) v = kb_sum_planes4(v, dr + i, n_delta, delta_stride);
+            if (write_back) *(float4*)(xr + i) = v;
+            *(float4*)(sv + i) = v;
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < E; i += NORM_THREADS) {
+            float v = xr[i];
+            if (n_delta > 0) v = kb_sum_planes(v, dr + i, n_delta, delta_stride);
+            if (write_back) xr[i] = v;
+            sv[i] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = kb_warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -94,20 +135,29 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
                               int write_back, int* status, cudaStream_t st) {
     if (n_out <= 0) return 0;
     size_t sm = (size_t)E * sizeof(float);
-    if (sm > 200 * 1024) return (int)cudaErrorInvalidValue;
-#define KB_NORM(TY, TW)                                                                                       \
-    do {                                                                                                      \
-        if (sm > 48 * 1024)                                                                                   \
-            cudaFuncSetAttribute(k_add_rmsnorm<TY, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-        k_add_rmsnorm<TY, TW><<<n_out, NORM_THREADS, sm, st>>>(x, delta, n_delta, (size_t)delta_stride, (const TW*)w,  \
-                                                      eps, (TY*)y, rows, T, E, write_back, status);           \
+    if (E > NORM_MAX_E) return (int)cudaErrorInvalidValue;
+    const bool vec = (E % 4 == 0) && (((uintptr_t)x) % 16 == 0) && (((uintptr_t)delta) % 16 == 0) &&
+                     (delta_stride % 4 == 0);
+    cudaError_t e = cudaSuccess;
+#define KB_NORM1(TY, TW, V)                                                                                      \
+    do {                                                                                                         \
+        if (sm > 48 * 1024)                                                                                      \
+            cudaFuncSetAttribute(k_add_rmsnorm<TY, TW, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+        e = kb_launch(k_add_rmsnorm<TY, TW, V>, n_out, NORM_THREADS, sm, st, x, delta, n_delta,                  \
+                      (size_t)delta_stride, (const TW*)w, eps, (TY*)y, rows, T, E, write_back, status);          \
+    } while (0)
+#define KB_NORM(TY, TW)                \
+    do {                               \
+        if (vec) KB_NORM1(TY, TW, true); \
+        else KB_NORM1(TY, TW, false);    \
     } while (0)
     if (ydtype == KB_F32 && wdtype == KB_F32) KB_NORM(float, float);
     else if (ydtype == KB_F32) KB_NORM(float, bf16);
     else if (wdtype == KB_F32) KB_NORM(bf16, float);
     else KB_NORM(bf16, bf16);
 #undef KB_NORM
-    KB_LAUNCH_RET();
+#undef KB_NORM1
+    return (int)e;
 }
 
 // ------------------------------------------------------------------------------------------------ matrix product
@@ -121,6 +171,8 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const TA* __restrict__ A, con
         TC* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
     __shared__ float As[GS_BK][GS_BM + 1];
     __shared__ float Ws[GS_BK][GS_BN + 1];
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     float acc[4][4];
@@ -168,7 +220,7 @@ extern "C" int kb_gemm_simt(const void* A, int adtype, const void* W, int wdtype
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
 #define KB_G(TA, TW, TC) \
-    k_gemm_simt<TA, TW, TC><<<grid, 256, 0, st>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc)
+    kb_launch(k_gemm_simt<TA, TW, TC>, grid, 256, 0, st, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc)
     int code = adtype * 4 + wdtype * 2 + cdtype;
     switch (code) {
         case 0: KB_G(float, float, float); break;
@@ -195,6 +247,8 @@ __global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t pl
         T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
         const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
         int hd, KbCacheView cv, int* status) {
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const int p = pos[t];
     const TIN* src = in + (size_t)t * ld_in + (size_t)h * hd;
@@ -251,7 +305,7 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
     dim3 grid(T, nh + 2 * nkv);
     int thr = hd / 2 < 32 ? 32 : (hd / 2 > 128 ? 128 : ((hd / 2 + 31) / 32) * 32);
 #define KB_RS(TIN, T_)                                                                                        \
-    k_rope_store<TIN, T_><<<grid, thr, 0, st>>>((const TIN*)in, n_planes, (size_t)plane_stride, ld_in,        \
+    kb_launch(k_rope_store<TIN, T_>, grid, thr, 0, st, (const TIN*)in, n_planes, (size_t)plane_stride, ld_in,        \
                                                 (T_*)qout, ldq, inv_freq, rot, pos, seq, slot, nh, nkv, hd,   \
                                                 cv, status)
     if (in_dtype == KB_F32 && dtype == KB_F32) KB_RS(float, float);
@@ -273,6 +327,8 @@ __global__ void __launch_bounds__(128) k_attn_generic(const T* __restrict__ q, i
         int ldo, const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int Tn,
         int nh, int group, int hd, float scale, int window, KbCacheView cv, int* status) {
     __shared__ float qs[4][AG_MAX_HD];
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * 4 + warp;
     if (item >= (long long)Tn * nh) return;
@@ -345,10 +401,10 @@ extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int
     long long items = (long long)T * nh;
     int grid = (int)((items + 3) / 4);
     if (dtype == KB_F32)
-        k_attn_generic<float><<<grid, 128, 0, st>>>((const float*)q, ldq, (float*)out, ldo, pos, seq, slot, T, nh,
+        kb_launch(k_attn_generic<float>, grid, 128, 0, st, (const float*)q, ldq, (float*)out, ldo, pos, seq, slot, T, nh,
                                                    nh / nkv, hd, scale, window, cv, status);
     else
-        k_attn_generic<bf16><<<grid, 128, 0, st>>>((const bf16*)q, ldq, (bf16*)out, ldo, pos, seq, slot, T, nh,
+        kb_launch(k_attn_generic<bf16>, grid, 128, 0, st, (const bf16*)q, ldq, (bf16*)out, ldo, pos, seq, slot, T, nh,
                                                   nh / nkv, hd, scale, window, cv, status);
     KB_LAUNCH_RET();
 }
@@ -358,6 +414,8 @@ extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int
 template <typename TIN, typename T>
 __global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_stride, T* __restrict__ out, int F,
                          long long total) {
+    kb_pdl_launch();
+    kb_pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / F;
@@ -388,11 +446,11 @@ extern "C" int kb_swiglu(const void* gu, int in_dtype, int n_planes, long long p
     if (total <= 0) return 0;
     int grid = (int)((total + 255) / 256);
     if (in_dtype == KB_F32 && dtype == KB_F32)
-        k_swiglu<float, float><<<grid, 256, 0, st>>>((const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total);
+        kb_launch(k_swiglu<float, float>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total);
     else if (in_dtype == KB_F32 && dtype == KB_BF16)
-        k_swiglu<float, bf16><<<grid, 256, 0, st>>>((const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
+        kb_launch(k_swiglu<float, bf16>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
     else if (in_dtype == KB_BF16 && dtype == KB_BF16)
-        k_swiglu<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
+        kb_launch(k_swiglu<bf16, bf16>, grid, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
     else return (int)cudaErrorInvalidValue;
     KB_LAUNCH_RET();
 }

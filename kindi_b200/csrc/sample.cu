@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(const float* __restrict__
     __shared__ unsigned long long s_red[32];
     __shared__ unsigned s_sel[2];
     __shared__ unsigned long long s_sel64[2];
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* z = logits + (size_t)row * ld;
     float zmax;
@@ -210,7 +212,7 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(const float* __restrict__
 extern "C" int kb_sample(const float* logits, long long ld, int R, int V, float temperature, int top_k, float top_p,
                          float min_p, int hf_order, const float* uniform, int* out, cudaStream_t st) {
     if (R <= 0) return 0;
-    k_sample<<<R, SM_THREADS, 0, st>>>(logits, ld, V, temperature, top_k, top_p, min_p, hf_order, uniform, out);
+    kb_launch(k_sample, R, SM_THREADS, 0, st, logits, ld, V, temperature, top_k, top_p, min_p, hf_order, uniform, out);
     KB_LAUNCH_RET();
 }
 
@@ -218,6 +220,8 @@ extern "C" int kb_sample(const float* logits, long long ld, int R, int V, float 
 // (kindi/sampling.py:117-123). recent: [R][n_recent], each row's distinct recent tokens, padded with -1.
 __global__ void k_penalize(float* __restrict__ logits, long long ld, int V, const int* __restrict__ recent,
                            int n_recent, float rp) {
+    kb_pdl_launch();
+    kb_pdl_wait();
     const int row = blockIdx.x;
     float* z = logits + (size_t)row * ld;
     for (int j = threadIdx.x; j < n_recent; j += blockDim.x) {
@@ -232,6 +236,6 @@ __global__ void k_penalize(float* __restrict__ logits, long long ld, int V, cons
 extern "C" int kb_penalize(float* logits, long long ld, int R, int V, const int* recent, int n_recent, float rp,
                            cudaStream_t st) {
     if (R <= 0 || n_recent <= 0) return 0;
-    k_penalize<<<R, 256, 0, st>>>(logits, ld, V, recent, n_recent, rp);
+    kb_launch(k_penalize, R, 256, 0, st, logits, ld, V, recent, n_recent, rp);
     KB_LAUNCH_RET();
 }

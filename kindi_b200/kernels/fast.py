@@ -79,8 +79,9 @@ def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages
         return False
     g = nh // nkv
     if ctx.decode and g <= 16:
-        # position splits: about three CTAs per SM over all (sequence, key/value head) pairs
-        splits = max(1, min(64, -(-3 * N_SM // (ctx.B * nkv))))
+        # position splits: two CTAs fit an SM, so as many splits as fill one wave of 2 x 148 CTAs over all
+        # (sequence, key/value head) pairs, never more (a second, partly filled wave would cost a whole one)
+        splits = max(1, min(64, 2 * N_SM // (ctx.B * nkv)))
         K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table,
                    n_pages, decode=True, grid_x=splits, status=ctx.status)
         return True

@@ -64,9 +64,16 @@ def load(verbose: bool = True):
             raise KernelError("kindi_b200: the kernel library %s lacks %s" % (path, name))
         fn.argtypes = args
         fn.restype = c_int
+    lib.kb_set_pdl.argtypes = [c_int]
+    lib.kb_set_pdl.restype = None
     lib._path = path
     _lib = lib
     return lib
+
+
+def set_pdl(on: bool) -> None:
+    """launch kernels with programmatic dependent launch (the default) or strictly one after another"""
+    load().kb_set_pdl(1 if on else 0)
 
 
 def library_file() -> str:
