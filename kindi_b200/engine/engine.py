@@ -71,7 +71,7 @@ class Engine:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
-        self.cuda_graphs = bool(cuda_graphs)
+        self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self.graph_replays = 0
         self._graph_warm = set()

@@ -101,6 +101,9 @@ class Part:
     run's dtype/device and a ``WeightView``."""
 
     category = ""
+    # False for a part whose forward reads the step's host-side numbers (h_slot, h_q_start, h_kv_len, max_kv) or
+    # launches work that cannot be recorded: the engine then runs every step launch by launch
+    graph_safe = True
 
     @classmethod
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:

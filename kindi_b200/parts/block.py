@@ -49,6 +49,7 @@ class PreNormBlock(Block):
                                                         device=device)
         self.norm1, self.mixer, self.norm2, self.feed_forward = (make(r) for r in
                                                                  ("norm1", "mixer", "norm2", "feed_forward"))
+        self.graph_safe = all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
 
     def forward(self, ctx: StepContext, x, pending: Optional[Branch]) -> Optional[Branch]:
         y = self.norm1.add_norm(ctx, x, pending)

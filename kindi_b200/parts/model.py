@@ -52,6 +52,7 @@ class DecoderModel:
         self.final_norm = part_class("norm", spec.final_norm.kind)(
             spec.final_norm, spec.width, WeightView(tensors, spec.final_norm_prefix), dtype=dtype, device=device)
         self.head = self.embedding if spec.head_name is None else tensors[spec.head_name]
+        self.graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
 
     def forward(self, ctx: StepContext, rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """run the step's tokens through every scheduled layer (keys, values and state are stored on the way);

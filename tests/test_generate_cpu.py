@@ -1,0 +1,130 @@
+"""The generation loop's decisions, driven by a stand-in stepper: batches, stop tokens, lengths, slots."""
+import pytest
+
+from kindi_b200.config.runtime import SamplingParams
+from kindi_b200.engine.batch import StepEntry, layout, pack
+from kindi_b200.engine.generate import PromptTooLong, generate, max_new_tokens, plan_batches
+
+
+class FakeStepper:
+    """the next token of a sequence is (sum of its tokens so far) mod 97; it records every step"""
+
+    def __init__(self, ctx=4096, max_batch=4, n_slots=4):
+        self.ctx, self.max_batch = ctx, max_batch
+        self.free_slots = list(range(n_slots))
+        self.held = {}
+        self.steps = []
+        self.sums = {}
+
+    def alloc(self):
+        s = self.free_slots.pop()
+        assert s not in self.held
+        self.held[s] = True
+        self.sums[s] = 0
+        return s
+
+    def free(self, slot):
+        assert self.held.pop(slot)                  # freeing twice fails here
+        self.free_slots.append(slot)
+
+    def run(self, entries, params, seq_ids, histories):
+        assert len({e.slot for e in entries}) == len(entries) and all(e.slot in self.held for e in entries)
+        self.steps.append([(e.slot, len(e.tokens)) for e in entries])
+        out = []
+        for e, h in zip(entries, histories):
+            self.sums[e.slot] += sum(e.tokens)
+            assert self.sums[e.slot] == sum(h)      # the loop fed every token exactly once
+            out.append(self.sums[e.slot] % 97)
+        return out
+
+
+def _expect(prompt, n, stop=()):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        t = sum(seq) % 97
+        if t in stop:
+            return out, "stop"
+        out.append(t)
+        seq.append(t)
+    return out, "length"
+
+
+def test_unequal_prompts_stop_tokens_and_early_ends():
+    st = FakeStepper()
+    prompts = [[1, 2, 3], [50], [7] * 20, [9, 9]]
+    p = SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=(31,))
+    res = generate(st, prompts, p, stop_token_ids=[4])
+    for i, pr in enumerate(prompts):
+        want, fin = _expect(pr, 12, stop=(31, 4))
+        assert res.tokens[i] == want and res.finish[i] == fin
+    assert st.steps[0] == [(s, len(pr)) for (s, _), pr in zip(st.steps[0], prompts)]        # all prompts in one step
+    assert all(n == 1 for step in st.steps[1:] for _, n in step)                              # then one token each
+    sizes = [len(s) for s in st.steps]
+    assert sizes == sorted(sizes, reverse=True) and not st.held                               # shrinking batch, all freed
+    assert res.stats.generated_tokens == sum(len(t) for t in res.tokens) and res.stats.batches == 1
+
+
+def test_batches_one_after_another_reuse_slots():
+    st = FakeStepper(max_batch=2, n_slots=2)
+    prompts = [[i + 1] * (i + 1) for i in range(5)]
+    res = generate(st, prompts, SamplingParams(temperature=0.0, max_tokens=3))
+    assert res.stats.batches == 3 and not st.held
+    for i, pr in enumerate(prompts):
+        assert res.tokens[i] == _expect(pr, 3)[0]
+    firsts = [s for s in st.steps if any(n > 1 for _, n in s) or s == st.steps[0]]
+    assert {slot for step in st.steps for slot, _ in step} == {0, 1}                          # the same two slots
+
+
+def test_limits():
+    assert max_new_tokens(10, 1024, 100) == 90 and max_new_tokens(10, 5, 100) == 5
+    with pytest.raises(PromptTooLong):
+        max_new_tokens(100, 5, 100)
+    with pytest.raises(ValueError):
+        max_new_tokens(0, 5, 100)
+    # the cache holds 4 pages: two requests of 100 + 28 tokens fit (2 pages each), a third starts a new batch
+    assert plan_batches([100, 100, 100], [28, 28, 28], ctx=256, max_batch=8) == [[0, 1], [2]]
+    assert plan_batches([1] * 5, [1] * 5, ctx=4096, max_batch=2) == [[0, 1], [2, 3], [4]]
+    st = FakeStepper(ctx=64)
+    with pytest.raises(PromptTooLong):
+        generate(st, [[1] * 64], SamplingParams(temperature=0.0))
+    res = generate(st, [[1] * 60], SamplingParams(temperature=0.0, max_tokens=1000))
+    assert len(res.tokens[0]) == 4 and res.finish == ["length"]                               # ctx - len(prompt)
+
+
+def test_cancel_and_callback():
+    st = FakeStepper()
+    seen = []
+    n = {"steps": 0}
+
+    def cancel():
+        n["steps"] += 1
+        return n["steps"] >= 3
+    res = generate(st, [[1, 2], [3]], SamplingParams(temperature=0.0, max_tokens=50), on_tokens=seen.append,
+                   cancel=cancel)
+    assert res.finish == ["stop", "stop"] and all(len(t) == 3 for t in res.tokens) and not st.held
+    assert len(seen) == 3 and all(set(d) == {0, 1} for d in seen)
+
+
+def test_slots_are_freed_when_a_step_fails():
+    class Boom(FakeStepper):
+        def run(self, *a):
+            if len(self.steps) == 2:
+                raise RuntimeError("boom")
+            return super().run(*a)
+    st = Boom()
+    with pytest.raises(RuntimeError):
+        generate(st, [[1], [2]], SamplingParams(temperature=0.0, max_tokens=9))
+    assert not st.held
+
+
+def test_pack_arithmetic():
+    ps = pack([StepEntry(3, (5, 6, 7), (0, 2)), StepEntry(1, (9,), (0,))], length_before=[10, 64])
+    seg = lambda n: ps.meta[ps.off[n][0]: ps.off[n][0] + ps.off[n][1]].tolist()         # noqa: E731
+    assert seg("tok") == [5, 6, 7, 9] and seg("pos") == [10, 11, 12, 64] and seg("seq") == [0, 0, 0, 1]
+    assert seg("slot") == [3, 1] and seg("q_start") == [0, 3, 4] and seg("kv_len") == [13, 65]
+    assert seg("rows") == [0, 2, 3] and (ps.T, ps.B, ps.R) == (4, 2, 3) and not ps.decode and ps.max_kv == 65
+    assert pack([StepEntry(0, (1,), (0,)), StepEntry(2, (1,), (0,))], [5, 6]).decode
+    assert layout(4, 2, 3) == layout(4, 2, 3) and all(a % 4 == 0 for a, _ in layout(5, 3, 2)[0].values())
+    for bad in ([StepEntry(0, (), ())], [StepEntry(0, (1,), (1,))], [StepEntry(0, (1,)), StepEntry(0, (2,))], []):
+        with pytest.raises(ValueError):
+            pack(bad, [0] * len(bad))

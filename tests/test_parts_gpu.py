@@ -1,0 +1,235 @@
+"""Each part alone against its plain function; and that parts defined outside the package (a mixer with state of its
+own), a layer that runs twice and a layer that reads another layer's keys and values can be registered, built and
+stepped without a change to the package."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as P
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(tmp_path, name, dtype, **kw):
+    from kindi_b200.engine.engine import Engine
+    return Engine(tiny.make_model(tmp_path, name, dtype), ctx=1024, dtype=dtype, max_batch=4, **kw)
+
+
+def _ctx(eng, seqs):
+    """a step context for whole sequences of the given lengths that start now"""
+    from kindi_b200.engine.batch import StepEntry, pack
+    entries = [StepEntry(eng.alloc(), tuple(range(n)), ()) for n in seqs]
+    ps = pack(entries, [0] * len(entries))
+    for e, n in zip(entries, ps.h_kv_len):
+        eng.cache.reserve(e.slot, n)
+    eng.cache.flush()
+    ctx = eng._context(ps)
+    ctx.entry = eng.spec.schedule[0]
+    return ctx
+
+
+def _rel(a, b):
+    return float((a.double().cpu() - b.double()).abs().max() / (b.double().abs().max() + 1e-30))
+
+
+TOL = {"float32": 3e-6, "bfloat16": 1.2e-2}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C", "E"])
+def test_norm_mixer_feed_forward_block_alone(tmp_path, name, dtype):
+    from kindi_b200.parts.base import Branch
+    eng = _engine(tmp_path, name, dtype)
+    m = P.load_model(tiny.make_model(tmp_path, name, dtype))
+    seqs = [70, 1, 9]
+    T, E = sum(seqs), eng.spec.width
+    ctx = _ctx(eng, seqs)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, E, generator=g)
+    planes = torch.randn(3, T, E, generator=g) * 0.1
+    blk = eng.model.blocks[0]
+    w = m["w"]
+    # ---- norm, with three pending planes, all rows and then a subset of rows
+    xd = x.cuda().clone()
+    y = blk.norm1.add_norm(ctx, xd, Branch(planes.cuda()))
+    xs = x.double() + planes.double().sum(0)
+    want = P.rms_norm(xs, w["model.layers.0.input_layernorm.weight"], m["eps"])
+    assert _rel(xd, xs) < 1e-6 and _rel(y.float(), want) < (1e-6 if dtype == "float32" else 6e-3)
+    rows = torch.tensor([5, 70, 79, 0], dtype=torch.int32).cuda()
+    y2 = blk.norm1.add_norm(ctx, xd, None, rows=rows)
+    assert torch.equal(y2, y[rows.long()])
+    # ---- mixer alone: whole sequences, so the plain attention of each sequence is the reference
+    yin = (torch.randn(T, E, generator=g) * 0.5).to(eng.dtype)
+    br = blk.mixer.forward(ctx, yin.cuda())
+    got = br.parts.sum(0)
+    H, KV, d = m["heads"], m["kv_heads"], m["head_dim"]
+    at = 0
+    for n in seqs:
+        yy = yin[at:at + n].double()
+        cos, sin = P.rope_tables(torch.arange(n), d, m["theta"], torch.float64)
+        q = P.rope_rotate_half((yy @ w["model.layers.0.self_attn.q_proj.weight"].T).view(n, H, d), cos, sin)
+        k = P.rope_rotate_half((yy @ w["model.layers.0.self_attn.k_proj.weight"].T).view(n, KV, d), cos, sin)
+        v = (yy @ w["model.layers.0.self_attn.v_proj.weight"].T).view(n, KV, d)
+        window = m["window"] if (m["window"] and (m["layer_types"] is None or m["layer_types"][0] == "sliding_attention")) else None
+        a = P.attention(q, k, v, 1 / math.sqrt(d), window).reshape(n, H * d)
+        assert _rel(got[at:at + n], a @ w["model.layers.0.self_attn.o_proj.weight"].T) < TOL[dtype]
+        at += n
+    # ---- feed-forward alone
+    br = blk.feed_forward.forward(ctx, yin.cuda())
+    want = P.swiglu_mlp(yin.double(), w["model.layers.0.mlp.gate_proj.weight"], w["model.layers.0.mlp.up_proj.weight"],
+                        w["model.layers.0.mlp.down_proj.weight"])
+    assert _rel(br.parts.sum(0), want) < TOL[dtype]
+    # ---- the whole block: residual in, residual + pending out
+    for s in list(ctx.h_slot):
+        eng.free(s)
+    ctx = _ctx(eng, seqs)
+    xd = x.cuda().clone()
+    pend = blk.forward(ctx, xd, None)
+    got = xd + pend.parts.sum(0)
+    at = 0
+    for n in seqs:
+        cos, sin = P.rope_tables(torch.arange(n), d, m["theta"], torch.float64)
+        assert _rel(got[at:at + n], P.decoder_layer(m, 0, x[at:at + n].double(), cos, sin)) < TOL[dtype]
+        at += n
+    eng.check_status()
+
+
+def test_embedding_and_position_encoding_alone(tmp_path):
+    from kindi_b200.kernels import lib as K
+    from kindi_b200.parts.rope import Rotary
+    from kindi_b200.config.spec import PartSpec
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    table = torch.randn(37, 24).to(torch.bfloat16).cuda()
+    tok = torch.tensor([0, 36, 5, 5], dtype=torch.int32).cuda()
+    out = torch.empty(4, 24, device="cuda")
+    K.embed(table, tok, out, st)
+    assert torch.equal(out, table.float()[tok.long()]) and int(st.item()) == 0
+    K.embed(table, torch.tensor([37, -1, 3, 0], dtype=torch.int32).cuda(), out, st)
+    assert int(st.item()) == K.ST_BAD_TOKEN and float(out[:2].abs().sum()) == 0.0    # skipped, reported, no fault
+    # rotary: the table of the part and the rotation of the kernel against the plain functions, partial rotation too
+    for hd, rot, base in [(16, 16, 10000.0), (48, 32, 500000.0), (128, 128, 7e7)]:
+        rp = Rotary(PartSpec("rotary", {"base": base, "rotary_dim": rot}), 0, None, dtype=torch.float32, device="cuda")
+        i = torch.arange(rot // 2, dtype=torch.float64)
+        assert torch.equal(rp.inv_freq.cpu(), (base ** (-2 * i / rot)).float())
+        pos = torch.tensor([0, 1, 77, 8191, 40000], dtype=torch.int32)
+        x = torch.randn(5, 3 * hd)
+        xd = x.cuda().clone()
+        seq = torch.zeros(5, dtype=torch.int32).cuda()
+        table_ = torch.zeros(1, 1, dtype=torch.int32).cuda()
+        st.zero_()
+        K.rope_store(xd, xd, rp.inv_freq, rot, pos.cuda(), seq, seq[:1], 3, 0, hd, None, table_, 1, st)
+        cos, sin = P.rope_tables(pos, rot, base, torch.float64)
+        want = P.rope_rotate_half(x.double().view(5, 3, hd), cos, sin).reshape(5, 3 * hd)
+        assert _rel(xd, want) < 1e-6
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# a mixer defined here, not in the package: y_t = W * mean(x_0 .. x_t). Its state per sequence is the running sum and
+# the count; it is written in plain PyTorch and uses the step's host-side numbers, so it declares graph_safe = False.
+def _toy_parts():
+    from kindi_b200.config.registry import register_part
+    from kindi_b200.parts.base import Branch, Mixer, StateNeed
+
+    class RunningMean(Mixer):
+        graph_safe = False
+
+        @classmethod
+        def tensor_shapes(cls, spec, width):
+            return {"mix.weight": (width, width)}
+
+        @classmethod
+        def cache_need(cls, spec, width):
+            return StateNeed((width + 1,))
+
+        def __init__(self, spec, width, weights, *, dtype, device):
+            super().__init__(spec, width, weights, dtype=dtype, device=device)
+            self.w = weights("mix.weight").float()
+
+        def forward(self, ctx, y):
+            state = ctx.cache.state_view(ctx.entry.cache)
+            out = torch.empty((1, ctx.T, self.width), dtype=torch.float32, device=y.device)
+            for b, slot in enumerate(ctx.h_slot):
+                a, e = ctx.h_q_start[b], ctx.h_q_start[b + 1]
+                run = state[slot, :-1] + torch.cumsum(y[a:e].float(), dim=0)
+                cnt = state[slot, -1] + torch.arange(1, e - a + 1, device=y.device, dtype=torch.float32)
+                out[0, a:e] = (run / cnt[:, None]) @ self.w.T
+                state[slot, :-1] = run[-1]
+                state[slot, -1] = cnt[-1]
+            return Branch(out)
+
+    register_part("mixer", "toy_running_mean", RunningMean, replace=True)
+
+
+def _toy_spec(width=64, vocab=97):
+    from kindi_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    norm = PartSpec("rmsnorm", {"eps": 1e-5})
+    ffn = PartSpec("swiglu", {"intermediate": 96})
+    att = PartSpec("attention", {"n_heads": 4, "n_kv_heads": 2, "head_dim": 16, "window": None,
+                                 "position": PartSpec("rotary", {"base": 10000.0, "rotary_dim": 16})})
+    toy = PartSpec("toy_running_mean", {})
+    layers = (LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": att, "norm2": norm, "feed_forward": ffn}), "l0."),
+              LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": toy, "norm2": norm, "feed_forward": ffn}), "l1."),
+              LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": att, "norm2": norm, "feed_forward": ffn}), "l2."))
+    # layer 0 runs twice (its second run owns cache entry 2); layer 2 reads the keys and values of the first run
+    schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(2, 3, reads_cache_of=0))
+    spec = ModelSpec(architecture="toy", vocab_size=vocab, width=width, layers=layers, schedule=schedule,
+                     final_norm=norm, embedding_name="emb", final_norm_prefix="fn.", head_name=None)
+    spec.validate()
+    return spec
+
+
+def _toy_plain(spec, w, tokens):
+    """the toy model on one whole sequence, in float64, from the plain part functions"""
+    w = {k: v.double().cpu() for k, v in w.items()}
+    n = len(tokens)
+    x = P.embedding(w["emb"], tokens)
+    cos, sin = P.rope_tables(torch.arange(n), 16, 10000.0, torch.float64)
+    kv = {}
+    for e in spec.schedule:
+        p = spec.layers[e.layer].prefix
+        y = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-5)
+        if spec.layers[e.layer].block["mixer"].kind == "attention":
+            q = P.rope_rotate_half((y @ w[p + "self_attn.q_proj.weight"].T).view(n, 4, 16), cos, sin)
+            if e.reads_cache_of is None:
+                k = P.rope_rotate_half((y @ w[p + "self_attn.k_proj.weight"].T).view(n, 2, 16), cos, sin)
+                kv[e.cache] = (k, (y @ w[p + "self_attn.v_proj.weight"].T).view(n, 2, 16))
+            k, v = kv[e.cache if e.reads_cache_of is None else e.reads_cache_of]
+            a = P.attention(q, k, v, 0.25).reshape(n, 64) @ w[p + "self_attn.o_proj.weight"].T
+        else:
+            mean = torch.cumsum(y, 0) / torch.arange(1, n + 1, dtype=torch.float64)[:, None]
+            a = mean @ w[p + "self_attn.mix.weight"].T
+        x = x + a
+        y = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+        x = x + P.swiglu_mlp(y, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return P.rms_norm(x, w["fn.weight"], 1e-5) @ w["emb"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 1.5e-2)])
+def test_toy_mixer_with_state_repeated_layer_and_shared_cache(tmp_path, dtype, tol):
+    from kindi_b200.engine.engine import Engine
+    from kindi_b200.parts.model import cache_needs, expected_tensors
+    from kindi_b200.weights.random_init import random_tensors
+    _toy_parts()
+    spec = _toy_spec()
+    shapes = expected_tensors(spec)
+    assert "l1.self_attn.mix.weight" in shapes and "l2.self_attn.k_proj.weight" in shapes
+    needs = cache_needs(spec)
+    assert [type(n).__name__ for n in needs] == ["KVNeed", "StateNeed", "KVNeed", "NoneType"]
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = random_tensors(shapes, seed=9, std=0.05, dtype=tdt)
+    eng = Engine(spec=spec, tensors=w, ctx=1024, dtype=dtype, max_batch=3)
+    assert not eng.cuda_graphs                                   # the toy mixer is not graph-safe
+    reqs = tiny.random_requests(97, [40, 7, 90, 3, 66], seed=4)
+    want = {r: _toy_plain(spec, w, t).numpy() for r, t in reqs.items()}
+    for steps in (tiny.trace_whole(reqs), tiny.trace_last_n(reqs, 32), tiny.trace_batched(reqs, batch=3, decode=10)):
+        out = str(tmp_path / ("o%d" % len(steps)))
+        tiny.run_replay(eng, steps, out)
+        got = tiny.collect(out, steps, 97)
+        for r, t in reqs.items():
+            mine = np.stack([got[(r, i)] for i in range(len(t))])
+            assert tiny.rel_err(mine, want[r]) < tol, (len(steps), r)
+        eng.cache.check()
+        assert eng.cache.slots.n_held == 0
