@@ -231,10 +231,20 @@ class _DecodeGraph:
         a, m = ps.off["rows"]
         rows = self.meta[a:a + m]
         self.graph = torch.cuda.CUDAGraph()
+        # Nothing but this library's launches may happen while the stream records: a garbage collection that frees
+        # pinned buffers of an earlier engine would query events, which invalidates a recording in the strict mode.
+        import gc
+        gc.collect()
         torch.cuda.synchronize()
         n0 = K.launch_count()
-        with torch.cuda.graph(self.graph):
-            self.logits = engine.model.forward(ctx, rows)
+        was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
+                self.logits = engine.model.forward(ctx, rows)
+        finally:
+            if was_on:
+                gc.enable()
         self.launches = K.launch_count() - n0        # recorded, not run
         K.add_launches(-self.launches)
 

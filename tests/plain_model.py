@@ -154,17 +154,20 @@ def sampling_distribution(z: np.ndarray, temperature: float, top_p: float, top_k
     """the token ids (best first) and probabilities the sampler draws from (kindi/sampling.py:91-114): keep the
     top_k best (0: all), then the shortest best-first prefix whose mass before each token is < top_p (probabilities
     at temperature 1, or at the temperature with order "hf"), then tokens with z >= z_max + ln(min_p), then
-    p = softmax((z - z_max) / temperature)"""
+    p = softmax((z - z_max) / temperature). Exact ties at a cut: the reference takes an arbitrary one of the tied
+    tokens (np.argpartition, kindi/sampling.py:97-98); this library keeps every token whose logit equals the last
+    kept one, so that the result does not depend on an order among equals."""
     z = np.asarray(z, dtype=np.float64)
     ids = np.argsort(-z, kind="stable")
     if top_k and top_k < len(ids):
-        ids = ids[:top_k]
+        ids = ids[z[ids] >= z[ids[top_k - 1]]]
     zs = z[ids]
     if top_p and top_p < 1.0:
         q = zs / temperature if order == "hf" else zs
         q = np.exp(q - q.max())
         q /= q.sum()
         keep = (np.cumsum(q) - q) < top_p
+        keep = zs >= zs[keep][-1]
         ids, zs = ids[keep], zs[keep]
     if min_p and min_p > 0.0:
         keep = zs >= zs.max() + np.log(min_p)
