@@ -216,8 +216,9 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "ahtx/kindi's Nanbeige engine needs CuPy (not installed, no index) and a quantised GGUF "
-                          "model file; it has no bf16 safetensors path and serves one request at a time"}))
+                          "ahtx/kindi is not pip-installable offline (no setup.py or pyproject.toml); its Nanbeige engine "
+                          "needs CuPy (not installed, no index) and a quantised GGUF model file, has no bf16 "
+                          "safetensors path and serves one request at a time"}))
         return 0
     if a.gpus != 1:
         print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
