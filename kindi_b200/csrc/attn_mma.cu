@@ -12,6 +12,7 @@
 //     (kindi/nbq.cu:635-649).
 // Head sizes 64 and 128; any number of heads and groups for prefill, groups up to 16 for decode. Other shapes run
 // the general kernel.
+#include <stdio.h>
 #include "sm100.cuh"
 
 #define AT_THREADS 160          // warps 0-3: MMA + softmax, warp 4: TMA producer
@@ -409,4 +410,57 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
         return (int)cudaGetLastError();
     }
     return 0;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory (declared in kindi_b200_noalloc.h; the reference has
+// no counterpart). Some hosts of this library may not call cudaMalloc at all: a plug-in that runs inside another
+// program's CUDA context under a fixed memory budget, a real-time loop that must not touch the allocator once it is
+// running, a process whose memory pool is owned by somebody else. kb_attn_mma above needs scratch for the partial
+// results of its position splits and takes it from its caller (who gets it from an allocator); this entry point runs
+// the same kernels with that scratch in the file-scope array below instead, so it allocates nothing: no cudaMalloc,
+// no cudaFree, no library routine that allocates. The caller still passes every input and output.
+//
+// The array is part of the loaded library: every GPU that loads it holds KB_STATIC_SCRATCH_FLOATS * 4 bytes (4 MiB)
+// until the process exits. A call needs B * nh * n_splits * (hd + 2) floats of it; a call that needs more is
+// refused (cudaErrorInvalidValue, with a line on stderr that gives both numbers) and launches nothing.
+// In host code the array's NAME is only a stand-in (a host-side shadow symbol), not a device address; the address
+// the kernels get is looked up with cudaGetSymbolAddress, once per device, on the first call made while that device is
+// current. That first call should therefore come before any stream capture (the lookup is not a stream operation).
+// All calls share the one array, and it keeps what the last call left there. Nothing in it has to start at zero:
+// every split of every (sequence, head) writes its maximum, its sum and its whole output row before the merge
+// reads them. Two calls that overlap on the GPU (different streams, or graphs replayed side by side) race on the
+// array; calls on one stream are ordered and safe.
+#define KB_STATIC_SCRATCH_FLOATS (1 << 20)
+static __device__ __align__(256) float g_attn_static_scratch[KB_STATIC_SCRATCH_FLOATS];
+
+extern "C" int kb_attn_decode_static(const void* q, int ldq, void* out, int ldo, const int* slot,
+                                     const int* q_start, const int* kv_len, int B, int nh, int nkv, int hd,
+                                     float scale, int window, void* pool, const int* table, int table_stride,
+                                     int n_pages, int n_splits, int* status, cudaStream_t st) {
+    static float* base_of_device[64] = {nullptr};
+    if (B <= 0) return 0;
+    if (n_splits < 1 || n_splits > 64 || nh <= 0 || hd <= 0) return (int)cudaErrorInvalidValue;
+    const long long need = (long long)B * nh * n_splits * (hd + 2);
+    if (need > (long long)KB_STATIC_SCRATCH_FLOATS) {
+        fprintf(stderr,
+                "kb_attn_decode_static: this call needs %lld floats of scratch (B %d x heads %d x splits %d x (head "
+                "size %d + 2)) and the static array holds %d; use fewer splits or a smaller batch, or kb_attn_mma "
+                "with scratch of your own\n", need, B, nh, n_splits, hd, KB_STATIC_SCRATCH_FLOATS);
+        return (int)cudaErrorInvalidValue;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!base_of_device[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e != cudaSuccess || !p) return (int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+        base_of_device[dev] = (float*)p;
+    }
+    float* part_o = base_of_device[dev];
+    float* part_ml = part_o + (size_t)B * nh * n_splits * hd;
+    return kb_attn_mma(q, ldq, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv, hd, scale, window, pool,
+                       table, table_stride, n_pages, 1, n_splits, status, st);
 }
