@@ -45,8 +45,9 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
     const int tilesP = (rowsP + TC_BM - 1) / TC_BM, tilesQ = (rowsQ + BN - 1) / BN;
     const int n_units = tilesP * tilesQ * n_splits;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
-    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;          // columns of one accumulator
-    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+    // two accumulators: the second starts at half of the allocation (a power of two of at least 2 x BN columns)
+    constexpr uint32_t TMEM_COLS = BN <= 16 ? 32 : BN <= 32 ? 64 : BN <= 64 ? 128 : BN <= 128 ? 256 : 512;
+    constexpr uint32_t ACC_COLS = TMEM_COLS / 2;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -281,6 +282,9 @@ extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int
         switch (bn) {
             case 64: TC_GO(64, 6, false);
             case 128: TC_GO(128, 6, false);
+            case 160: TC_GO(160, 5, false);
+            case 192: TC_GO(192, 5, false);
+            case 224: TC_GO(224, 4, false);
             case 256: TC_GO(256, 4, false);
             default: return (int)cudaErrorInvalidValue;
         }

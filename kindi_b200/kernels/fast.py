@@ -45,6 +45,20 @@ def _splits_for(m: int, n: int, k: int, bn: int) -> int:
     return best
 
 
+def _prefill_bn(m: int, n: int) -> int:
+    """the width of the weight side of a prefill tile: the one whose tiles fill whole rounds of the persistent CTAs
+    best (a round costs about its width; a partly filled last round costs a whole one)"""
+    if n <= 64:
+        return 64
+    best, best_cost = 128, None
+    for bn in (256, 224, 192, 160, 128):
+        units = -(-m // 128) * -(-n // bn)
+        cost = -(-units // N_SM) * (bn + 32)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = bn, cost
+    return best
+
+
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
     if not _tc_ok(a, w) or not out.is_contiguous():
         return False
@@ -52,7 +66,7 @@ def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
     if m <= SMALL_M:
         K.gemm_tc(a, w, out, swap=True, bn=_swap_bn(m), splits=1, status=status)
     else:
-        K.gemm_tc(a, w, out, swap=False, bn=256 if n >= 512 else 128 if n > 64 else 64, splits=1, status=status)
+        K.gemm_tc(a, w, out, swap=False, bn=_prefill_bn(m, n), splits=1, status=status)
     return True
 
 
@@ -69,7 +83,7 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
         K.gemm_tc(a, w, out, swap=True, bn=bn, splits=want, status=status)
         return out
     out = torch.empty((1, m, n), dtype=torch.float32, device=a.device)
-    K.gemm_tc(a, w, out[0], swap=False, bn=256 if n >= 512 else 128 if n > 64 else 64, splits=1, status=status)
+    K.gemm_tc(a, w, out[0], swap=False, bn=_prefill_bn(m, n), splits=1, status=status)
     return out
 
 

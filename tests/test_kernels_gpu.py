@@ -40,6 +40,7 @@ def test_gemm_simt(K, M, N, K_, dtype):
 TC_CASES = [
     (128, 256, 64, False, 256, 1), (128, 128, 128, False, 128, 1), (200, 300, 136, False, 128, 1),
     (2048, 512, 2560, False, 256, 1), (130, 72, 72, False, 64, 1), (257, 1000, 520, False, 256, 1),
+    (300, 700, 200, False, 160, 1), (129, 500, 136, False, 192, 1), (512, 2560, 320, False, 224, 1),
     (1, 128, 64, True, 16, 1), (8, 384, 2560, True, 16, 1), (8, 384, 2560, True, 16, 5), (17, 200, 264, True, 32, 3),
     (64, 331 * 8, 1096, True, 64, 4), (100, 256, 4096, True, 128, 8), (5, 130, 72, True, 16, 2),
 ]
