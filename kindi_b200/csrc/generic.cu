@@ -295,6 +295,104 @@ __global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t pl
     }
 }
 
+// The same operation with one block per row: cosine and sine of the row's angles are computed once into shared
+// memory and used by every head, and each thread moves two neighbouring elements (and their partners) at a time.
+// Taken for steps of 32 rows or more (fewer rows want the many small blocks of k_rope_store) when rot % 4 == 0,
+// hd % 2 == 0 and the rows are aligned for two-element accesses; values are computed by the
+// same expressions as in k_rope_store, so both give the same bits.
+template <typename T> struct Kb2;
+template <> struct Kb2<float> { typedef float2 type; };
+template <> struct Kb2<bf16> { typedef __nv_bfloat162 type; };
+__device__ __forceinline__ float2 kb_ld2(const float* p) { return *(const float2*)p; }
+__device__ __forceinline__ float2 kb_ld2(const bf16* p) { return __bfloat1622float2(*(const __nv_bfloat162*)p); }
+__device__ __forceinline__ void kb_st2(float* p, float2 v) { *(float2*)p = v; }
+__device__ __forceinline__ void kb_st2(bf16* p, float2 v) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(v.x, v.y); }
+
+template <typename TIN, typename T>
+__global__ void __launch_bounds__(256) k_rope_store_row(const TIN* __restrict__ in, int n_planes, size_t plane_stride,
+        int ld_in, T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
+        const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
+        int hd, KbCacheView cv, int* status) {
+    extern __shared__ float2 cs[];                  // [rot / 2]: (cos, sin) of the row's angles
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int t = blockIdx.x;
+    const int p = pos[t];
+    const int half = rot / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = __fmul_rn((float)p, inv_freq[i]);
+        cs[i] = make_float2(cosf(ang), sinf(ang));
+    }
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (nkv > 0) {
+        const int s = slot[seq[t]];
+        const int page = cv.table[(size_t)s * cv.table_stride + p / KB_PAGE];
+        if (page < 0 || page >= cv.n_pages) {
+            if (threadIdx.x == 0) atomicOr(status, KB_ST_BAD_PAGE);
+        } else {
+            kdst = (T*)cv.pool + kb_kv_offset(cv, page, 0, 0, p % KB_PAGE);
+            vdst = (T*)cv.pool + kb_kv_offset(cv, page, 1, 0, p % KB_PAGE);
+        }
+    }
+    __syncthreads();
+    const TIN* row = in + (size_t)t * ld_in;
+    auto rd2 = [&](int e) {                          // elements e, e + 1 of the row: the planes added in order
+        float2 v = kb_ld2(row + e);
+        for (int s0 = 1; s0 < n_planes; s0 += 8) {
+            float2 tt[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                tt[j] = (s0 + j < n_planes) ? kb_ld2(row + (size_t)(s0 + j) * plane_stride + e) : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (s0 + j < n_planes) {
+                    v.x += tt[j].x;
+                    v.y += tt[j].y;
+                }
+        }
+        return v;
+    };
+    const size_t head_stride = (size_t)KB_PAGE * hd;       // from one key/value head to the next inside a page
+    // rotated heads: query heads, then key heads; an item is two neighbouring pairs of one head
+    const int per_head = half / 2, n_rot = (nh + nkv) * per_head;
+    for (int it = threadIdx.x; it < n_rot; it += blockDim.x) {
+        const int h = it / per_head, i = (it % per_head) * 2;
+        T* dst;
+        if (h < nh) dst = qout + (size_t)t * ldq + (size_t)h * hd;
+        else if (kdst) dst = kdst + (size_t)(h - nh) * head_stride;
+        else continue;
+        const float2 a = rd2(h * hd + i), b = rd2(h * hd + i + half);
+        const float2 c0 = cs[i], c1 = cs[i + 1];
+        float2 lo, hi;
+        lo.x = __fsub_rn(__fmul_rn(a.x, c0.x), __fmul_rn(b.x, c0.y));
+        lo.y = __fsub_rn(__fmul_rn(a.y, c1.x), __fmul_rn(b.y, c1.y));
+        hi.x = __fadd_rn(__fmul_rn(b.x, c0.x), __fmul_rn(a.x, c0.y));
+        hi.y = __fadd_rn(__fmul_rn(b.y, c1.x), __fmul_rn(a.y, c1.y));
+        kb_st2(dst + i, lo);
+        kb_st2(dst + i + half, hi);
+    }
+    // what is only copied: the elements past the rotated part of q and k heads, and the value heads
+    const int tail2 = (hd - rot) / 2;
+    if (tail2 > 0) {
+        for (int it = threadIdx.x; it < (nh + nkv) * tail2; it += blockDim.x) {
+            const int h = it / tail2, i = rot + (it % tail2) * 2;
+            T* dst;
+            if (h < nh) dst = qout + (size_t)t * ldq + (size_t)h * hd;
+            else if (kdst) dst = kdst + (size_t)(h - nh) * head_stride;
+            else continue;
+            kb_st2(dst + i, rd2(h * hd + i));
+        }
+    }
+    if (vdst) {
+        const int hd2 = hd / 2;
+        for (int it = threadIdx.x; it < nkv * hd2; it += blockDim.x) {
+            const int h = it / hd2, i = (it % hd2) * 2;
+            kb_st2(vdst + (size_t)h * head_stride + i, rd2((nh + nkv + h) * hd + i));
+        }
+    }
+}
+
 // in: [n_planes][T][ld_in] (the planes are summed in order); in_dtype may be 32-bit planes with a bf16 cache / qout
 extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in,
                              void* qout, int dtype, int ldq, const float* inv_freq, int rot, const int* pos,
@@ -304,7 +402,16 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
     KbCacheView cv{pool, table, table_stride, n_pages, nkv, hd};
     dim3 grid(T, nh + 2 * nkv);
     int thr = hd / 2 < 32 ? 32 : (hd / 2 > 128 ? 128 : ((hd / 2 + 31) / 32) * 32);
+    const int in_el = in_dtype == KB_F32 ? 4 : 2, out_el = dtype == KB_F32 ? 4 : 2;
+    const bool by_row = T >= 32 && rot % 4 == 0 && hd % 2 == 0 && ld_in % 2 == 0 && ldq % 2 == 0 && plane_stride % 2 == 0 &&
+                        ((uintptr_t)in % (2 * in_el)) == 0 && ((uintptr_t)qout % (2 * out_el)) == 0 &&
+                        ((uintptr_t)pool % (2 * out_el)) == 0 && rot / 2 * 8 <= 32 * 1024;
 #define KB_RS(TIN, T_)                                                                                        \
+    if (by_row)                                                                                               \
+        kb_launch(k_rope_store_row<TIN, T_>, T, 256, (size_t)(rot / 2) * sizeof(float2), st, (const TIN*)in,   \
+                  n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos, seq, slot, nh,   \
+                  nkv, hd, cv, status);                                                                       \
+    else                                                                                                      \
     kb_launch(k_rope_store<TIN, T_>, grid, thr, 0, st, (const TIN*)in, n_planes, (size_t)plane_stride, ld_in,        \
                                                 (T_*)qout, ldq, inv_freq, rot, pos, seq, slot, nh, nkv, hd,   \
                                                 cv, status)
@@ -439,12 +546,84 @@ __global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_
     out[i] = kb_from_f<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// the same with a row per blockIdx.y and two neighbouring columns per thread (F even, aligned rows)
+template <typename TIN, typename T>
+__global__ void __launch_bounds__(256) k_swiglu2(const TIN* __restrict__ gu, int n_planes, size_t plane_stride,
+                                                  T* __restrict__ out, int F) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int c = (blockIdx.x * 256 + threadIdx.x) * 2;
+    if (c >= F) return;
+    const size_t t = blockIdx.y;
+    const TIN* g0 = gu + t * 2 * F + c;
+    float2 g = make_float2(0.f, 0.f), u = make_float2(0.f, 0.f);
+    for (int s0 = 0; s0 < n_planes; s0 += 4) {
+        float2 tg[4], tu[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const bool on = s0 + j < n_planes;
+            tg[j] = on ? kb_ld2(g0 + (size_t)(s0 + j) * plane_stride) : make_float2(0.f, 0.f);
+            tu[j] = on ? kb_ld2(g0 + (size_t)(s0 + j) * plane_stride + F) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (s0 + j < n_planes) {
+                g.x += tg[j].x;
+                g.y += tg[j].y;
+                u.x += tu[j].x;
+                u.y += tu[j].y;
+            }
+    }
+    kb_st2(out + t * F + c, make_float2(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y));
+}
+
+// bf16 rows in, bf16 out, eight columns per thread with 16-byte accesses; exp and the division by the fast
+// intrinsics (their error is far below one bf16 rounding)
+__global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* __restrict__ gu, bf16* __restrict__ out, int F) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+    if (c >= F) return;
+    const size_t t = blockIdx.y;
+    const uint4 gv = *(const uint4*)(gu + t * 2 * F + c), uv = *(const uint4*)(gu + t * 2 * F + F + c);
+    const __nv_bfloat162* g2 = (const __nv_bfloat162*)&gv;
+    const __nv_bfloat162* u2 = (const __nv_bfloat162*)&uv;
+    uint4 ov;
+    __nv_bfloat162* o2 = (__nv_bfloat162*)&ov;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+        o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x,
+                                      __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y);
+    }
+    *(uint4*)(out + t * F + c) = ov;
+}
+
 // gu: [n_planes][T][2F] (planes summed in order), 32-bit or the output's type
 extern "C" int kb_swiglu(const void* gu, int in_dtype, int n_planes, long long plane_stride, void* out, int dtype,
                          int T, int F, cudaStream_t st) {
     long long total = (long long)T * F;
     if (total <= 0) return 0;
     int grid = (int)((total + 255) / 256);
+    const int in_el = in_dtype == KB_F32 ? 4 : 2, out_el = dtype == KB_F32 ? 4 : 2;
+    if (in_dtype == KB_BF16 && dtype == KB_BF16 && n_planes == 1 && F % 8 == 0 && ((uintptr_t)gu % 16) == 0 &&
+        ((uintptr_t)out % 16) == 0 && T <= 65535) {
+        dim3 g8((F / 8 + 255) / 256, T);
+        kb_launch(k_swiglu8_bf16, g8, 256, 0, st, (const bf16*)gu, (bf16*)out, F);
+        KB_LAUNCH_RET();
+    }
+    if (F % 2 == 0 && plane_stride % 2 == 0 && ((uintptr_t)gu % (2 * in_el)) == 0 &&
+        ((uintptr_t)out % (2 * out_el)) == 0 && T <= 65535) {
+        dim3 g2((F / 2 + 255) / 256, T);
+        if (in_dtype == KB_F32 && dtype == KB_F32)
+            kb_launch(k_swiglu2<float, float>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F);
+        else if (in_dtype == KB_F32 && dtype == KB_BF16)
+            kb_launch(k_swiglu2<float, bf16>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F);
+        else if (in_dtype == KB_BF16 && dtype == KB_BF16)
+            kb_launch(k_swiglu2<bf16, bf16>, g2, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F);
+        else return (int)cudaErrorInvalidValue;
+        KB_LAUNCH_RET();
+    }
     if (in_dtype == KB_F32 && dtype == KB_F32)
         kb_launch(k_swiglu<float, float>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total);
     else if (in_dtype == KB_F32 && dtype == KB_BF16)
