@@ -213,6 +213,7 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=CONFIG_3B["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
+    ap.add_argument("--prefill-only", action="store_true", help="measure only the 2048-token prefill (for profiling)")
     a = ap.parse_args(argv)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -232,6 +233,12 @@ def main(argv=None) -> int:
         _K.set_pdl(False)
     max_b = max(a.batch, 1 if a.no_points else 64)
     ctx = max_b * (a.context + a.steps * 2 + a.warmup + 256) + PREFILL_TOKENS + 64
+    if a.prefill_only:
+        eng = build_engine(a.layers, PREFILL_TOKENS + 128, 2)
+        pms = bench_prefill(eng, 2, max(1, min(a.steps, 3)))
+        print(json.dumps({"prefill_only": True, "layers": a.layers, "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                          "value": round(PREFILL_TOKENS * 1000.0 / pms, 1)}))
+        return 0
     eng = build_engine(a.layers, ctx, max_b)
     for g in eng.cache.groups:
         g.pool.normal_(0.0, 1.0)

@@ -29,17 +29,19 @@ def wants_planes(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def _splits_for(m: int, n: int, k: int, bn: int) -> int:
-    """how many ways to split K so that the persistent CTAs (one per SM) finish together: the cost of a launch is
-    the number of rounds of units times the K blocks of a unit; more planes cost the consumer more reads"""
+    """how many ways to split K for the persistent CTAs (one per SM). Estimated time of a launch, in microseconds:
+    rounds of units times the K blocks of a unit (16 KB of weights each, at one SM's share of the memory bandwidth),
+    plus what the 32-bit planes cost to write and to read again by the consumer (they grow with the batch)"""
     tiles = -(-n // 128) * -(-m // bn)
     total_kb = -(-k // 64)
+    us_per_kb = 16384.0 / (6.6e6 / N_SM)
     best, best_cost = 1, None
     for s in range(1, min(16, total_kb) + 1):
         kbps = -(-total_kb // s)
         if -(-total_kb // kbps) != s or (s > 1 and kbps < 2):
             continue
         rounds = -(-tiles * s // N_SM)
-        cost = rounds * (kbps + 0.5) + 0.05 * s
+        cost = rounds * (kbps + 0.5) * us_per_kb + 2.0 * s * m * n * 4 / 6.6e6
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
