@@ -520,21 +520,22 @@ extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int
 // gu: [T][2F] = gate then up; out[t][i] = gate / (1 + exp(-gate)) * up (kindi/nbq.cu:461-467)
 template <typename TIN, typename T>
 __global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_stride, T* __restrict__ out, int F,
-                         long long total) {
+                         long long total, int group) {
     kb_pdl_launch();
     kb_pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / F;
     const int c = (int)(i % F);
+    const int gc = (c / group) * 2 * group + c % group;        // the gate's column; the up's is `group` further
     float g = 0.0f, u = 0.0f;
     for (int s0 = 0; s0 < n_planes; s0 += 4) {
         float tg[4], tu[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const bool on = s0 + j < n_planes;
-            tg[j] = on ? kb_to_f<TIN>(gu[(size_t)(s0 + j) * plane_stride + t * 2 * F + c]) : 0.0f;
-            tu[j] = on ? kb_to_f<TIN>(gu[(size_t)(s0 + j) * plane_stride + t * 2 * F + F + c]) : 0.0f;
+            tg[j] = on ? kb_to_f<TIN>(gu[(size_t)(s0 + j) * plane_stride + t * 2 * F + gc]) : 0.0f;
+            tu[j] = on ? kb_to_f<TIN>(gu[(size_t)(s0 + j) * plane_stride + t * 2 * F + gc + group]) : 0.0f;
         }
 #pragma unroll
         for (int j = 0; j < 4; j++)
@@ -549,13 +550,13 @@ __global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_
 // the same with a row per blockIdx.y and two neighbouring columns per thread (F even, aligned rows)
 template <typename TIN, typename T>
 __global__ void __launch_bounds__(256) k_swiglu2(const TIN* __restrict__ gu, int n_planes, size_t plane_stride,
-                                                  T* __restrict__ out, int F) {
+                                                  T* __restrict__ out, int F, int group) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int c = (blockIdx.x * 256 + threadIdx.x) * 2;
     if (c >= F) return;
     const size_t t = blockIdx.y;
-    const TIN* g0 = gu + t * 2 * F + c;
+    const TIN* g0 = gu + t * 2 * F + (c / group) * 2 * group + c % group;
     float2 g = make_float2(0.f, 0.f), u = make_float2(0.f, 0.f);
     for (int s0 = 0; s0 < n_planes; s0 += 4) {
         float2 tg[4], tu[4];
@@ -563,7 +564,7 @@ __global__ void __launch_bounds__(256) k_swiglu2(const TIN* __restrict__ gu, int
         for (int j = 0; j < 4; j++) {
             const bool on = s0 + j < n_planes;
             tg[j] = on ? kb_ld2(g0 + (size_t)(s0 + j) * plane_stride) : make_float2(0.f, 0.f);
-            tu[j] = on ? kb_ld2(g0 + (size_t)(s0 + j) * plane_stride + F) : make_float2(0.f, 0.f);
+            tu[j] = on ? kb_ld2(g0 + (size_t)(s0 + j) * plane_stride + group) : make_float2(0.f, 0.f);
         }
 #pragma unroll
         for (int j = 0; j < 4; j++)
@@ -579,13 +580,15 @@ __global__ void __launch_bounds__(256) k_swiglu2(const TIN* __restrict__ gu, int
 
 // bf16 rows in, bf16 out, eight columns per thread with 16-byte accesses; exp and the division by the fast
 // intrinsics (their error is far below one bf16 rounding)
-__global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* __restrict__ gu, bf16* __restrict__ out, int F) {
+__global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* __restrict__ gu, bf16* __restrict__ out, int F,
+                                                      int group) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
     if (c >= F) return;
     const size_t t = blockIdx.y;
-    const uint4 gv = *(const uint4*)(gu + t * 2 * F + c), uv = *(const uint4*)(gu + t * 2 * F + F + c);
+    const bf16* g0 = gu + t * 2 * F + (c / group) * 2 * group + c % group;
+    const uint4 gv = *(const uint4*)g0, uv = *(const uint4*)(g0 + group);
     const __nv_bfloat162* g2 = (const __nv_bfloat162*)&gv;
     const __nv_bfloat162* u2 = (const __nv_bfloat162*)&uv;
     uint4 ov;
@@ -599,37 +602,39 @@ __global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* __restrict__ g
     *(uint4*)(out + t * F + c) = ov;
 }
 
-// gu: [n_planes][T][2F] (planes summed in order), 32-bit or the output's type
+// gu: [n_planes][T][2F] (planes summed in order), 32-bit or the output's type. Columns come in groups: `group` gate
+// columns, then the `group` up columns of the same outputs (group == F: all gates, then all ups).
 extern "C" int kb_swiglu(const void* gu, int in_dtype, int n_planes, long long plane_stride, void* out, int dtype,
-                         int T, int F, cudaStream_t st) {
+                         int T, int F, int group, cudaStream_t st) {
+    if (group <= 0 || F % group) return (int)cudaErrorInvalidValue;
     long long total = (long long)T * F;
     if (total <= 0) return 0;
     int grid = (int)((total + 255) / 256);
     const int in_el = in_dtype == KB_F32 ? 4 : 2, out_el = dtype == KB_F32 ? 4 : 2;
-    if (in_dtype == KB_BF16 && dtype == KB_BF16 && n_planes == 1 && F % 8 == 0 && ((uintptr_t)gu % 16) == 0 &&
+    if (in_dtype == KB_BF16 && dtype == KB_BF16 && n_planes == 1 && F % 8 == 0 && group % 8 == 0 && ((uintptr_t)gu % 16) == 0 &&
         ((uintptr_t)out % 16) == 0 && T <= 65535) {
         dim3 g8((F / 8 + 255) / 256, T);
-        kb_launch(k_swiglu8_bf16, g8, 256, 0, st, (const bf16*)gu, (bf16*)out, F);
+        kb_launch(k_swiglu8_bf16, g8, 256, 0, st, (const bf16*)gu, (bf16*)out, F, group);
         KB_LAUNCH_RET();
     }
-    if (F % 2 == 0 && plane_stride % 2 == 0 && ((uintptr_t)gu % (2 * in_el)) == 0 &&
+    if (F % 2 == 0 && group % 2 == 0 && plane_stride % 2 == 0 && ((uintptr_t)gu % (2 * in_el)) == 0 &&
         ((uintptr_t)out % (2 * out_el)) == 0 && T <= 65535) {
         dim3 g2((F / 2 + 255) / 256, T);
         if (in_dtype == KB_F32 && dtype == KB_F32)
-            kb_launch(k_swiglu2<float, float>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F);
+            kb_launch(k_swiglu2<float, float>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, group);
         else if (in_dtype == KB_F32 && dtype == KB_BF16)
-            kb_launch(k_swiglu2<float, bf16>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F);
+            kb_launch(k_swiglu2<float, bf16>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, group);
         else if (in_dtype == KB_BF16 && dtype == KB_BF16)
-            kb_launch(k_swiglu2<bf16, bf16>, g2, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F);
+            kb_launch(k_swiglu2<bf16, bf16>, g2, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, group);
         else return (int)cudaErrorInvalidValue;
         KB_LAUNCH_RET();
     }
     if (in_dtype == KB_F32 && dtype == KB_F32)
-        kb_launch(k_swiglu<float, float>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total);
+        kb_launch(k_swiglu<float, float>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total, group);
     else if (in_dtype == KB_F32 && dtype == KB_BF16)
-        kb_launch(k_swiglu<float, bf16>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
+        kb_launch(k_swiglu<float, bf16>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total, group);
     else if (in_dtype == KB_BF16 && dtype == KB_BF16)
-        kb_launch(k_swiglu<bf16, bf16>, grid, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total);
+        kb_launch(k_swiglu<bf16, bf16>, grid, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total, group);
     else return (int)cudaErrorInvalidValue;
     KB_LAUNCH_RET();
 }

@@ -41,7 +41,7 @@ def _splits_for(m: int, n: int, k: int, bn: int) -> int:
         if -(-total_kb // kbps) != s or (s > 1 and kbps < 2):
             continue
         rounds = -(-tiles * s // N_SM)
-        cost = rounds * (kbps + 0.5) * us_per_kb + 2.0 * s * m * n * 4 / 6.6e6
+        cost = rounds * (kbps + 0.5) * us_per_kb + s * m * n * 4 / 6.6e6
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -87,6 +87,17 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
     out = torch.empty((1, m, n), dtype=torch.float32, device=a.device)
     K.gemm_tc(a, w, out[0], swap=False, bn=_prefill_bn(m, n), splits=1, status=status)
     return out
+
+
+def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
+    """out (bf16 [M, F]) = silu(g) * u for a prompt-sized step, finished inside the product's epilogue; w_grouped
+    [2F, K] holds 64 gate rows then the 64 up rows of the same outputs, group after group. False: not taken"""
+    m, n = a.shape[0], w_grouped.shape[0]
+    if m <= SMALL_M or not _tc_ok(a, w_grouped) or n % 128 or not out.is_contiguous() or (n // 2) % 8:
+        return False
+    bn = _prefill_bn(m, n)
+    K.gemm_tc(a, w_grouped, out, swap=False, bn=bn if bn in (128, 256) else 256, splits=1, status=status, swiglu=True)
+    return True
 
 
 def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages) -> bool:

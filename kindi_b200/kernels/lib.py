@@ -38,9 +38,9 @@ _SIGS = {
                       c_void_p],
     "kb_attn_generic": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
-    "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                   c_longlong, c_void_p, c_void_p],
+                   c_longlong, c_void_p, c_void_p, c_int],
     "kb_gemm_tc_splits": [c_int, c_int],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -203,32 +203,40 @@ def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nk
                                   n_pages, _p(status), _stream()), "attn_generic")
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
-    """out[T, F] = silu(g) * u with [g | u] = gu [T, 2F], or the sum of 32-bit planes gu [S, T, 2F]"""
+def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
+    """out[T, F] = silu(g) * u with gu [T, 2F] (or the sum of 32-bit planes gu [S, T, 2F]). The columns of gu come in
+    groups of ``group`` gate columns followed by the ``group`` up columns of the same outputs (0: all gates, then
+    all ups)"""
     _need_cuda(gu, out)
     T, F = out.shape
     planes = gu.shape[0] if gu.dim() == 3 else 1
     assert gu.shape[-2:] == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous()
-    _check(load().kb_swiglu(_p(gu), dt(gu), planes, T * 2 * F, _p(out), dt(out), T, F, _stream()), "swiglu")
+    _check(load().kb_swiglu(_p(gu), dt(gu), planes, T * 2 * F, _p(out), dt(out), T, F, group or F, _stream()),
+           "swiglu")
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,
-            status: torch.Tensor) -> None:
+            status: torch.Tensor, swiglu: bool = False) -> None:
     """out = a[M, K] @ w[N, K]^T on the tensor cores (bf16 in, fp32 accumulate). ``out`` is [M, N] (bf16 or fp32)
-    or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits)"""
+    or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits). ``swiglu`` (prefill form, bn 128 or 256):
+    w holds 64 gate rows then the 64 up rows of the same outputs, group after group, and ``out`` is the bf16
+    [M, N / 2] result silu(gate) * up"""
     _need_cuda(a, w, out)
     M, K = a.shape
     N = w.shape[0]
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert a.stride(1) == 1 and w.stride(1) == 1 and out.is_contiguous()
-    if out.dim() == 3:
+    if swiglu:
+        assert out.shape == (M, N // 2) and out.dtype == torch.bfloat16 and not swap and splits == 1 and N % 128 == 0
+        stride, ldc = 0, N // 2
+    elif out.dim() == 3:
         assert out.shape == (gemm_tc_splits(K, splits), M, N) and out.dtype == torch.float32
-        stride = M * N
+        stride, ldc = M * N, N
     else:
         assert out.shape == (M, N) and splits == 1
-        stride = 0
-    _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), N, 1 if swap else 0,
-                             bn, splits, stride, _p(status), _stream()), "gemm_tc")
+        stride, ldc = 0, N
+    _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, 1 if swap else 0,
+                             bn, splits, stride, _p(status), _stream(), 1 if swiglu else 0), "gemm_tc")
 
 
 def gemm_tc_splits(K: int, wanted: int) -> int:

@@ -183,3 +183,28 @@ def test_attention_mma_decode(K, nh, nkv, hd, window):
     err = _run_attention(K, "decode", torch.bfloat16, nh, nkv, hd, [1, 1], [900, 65], window=0, seed=nh + 9,
                          boost=(0, 0, 3))
     assert err < 1e-2
+
+
+@pytest.mark.parametrize("M,F,K_,bn", [(129, 64, 128, 128), (2048, 1024, 520, 256), (300, 320, 264, 256), (200, 192, 72, 128)])
+def test_gemm_tc_finishes_swiglu_in_its_epilogue(K, M, F, K_, bn):
+    g = torch.Generator(device="cuda").manual_seed(M + F + K_)
+    a = (torch.randn(M, K_, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    wg = (torch.randn(F, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(F, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    wgu = torch.stack([wg.view(F // 64, 64, K_), wu.view(F // 64, 64, K_)], dim=1).reshape(2 * F, K_).contiguous()
+    st = _status()
+    out = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+    K.gemm_tc(a, wgu, out, swap=False, bn=bn, splits=1, status=st, swiglu=True)
+    gg, uu = a.double() @ wg.double().T, a.double() @ wu.double().T
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    assert int(st.item()) == 0
+    assert _rel(out.float(), ref) < 6e-3
+    # the stand-alone kernel reads the same grouping, from bf16 rows and from 32-bit planes
+    rows = torch.empty(M, 2 * F, device="cuda", dtype=torch.bfloat16)
+    K.gemm_tc(a, wgu, rows, swap=False, bn=bn, splits=1, status=st)
+    h = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    K.swiglu(rows, h, 64)
+    assert _rel(h.float(), ref) < 1.5e-2
+    planes = rows.float()[None].contiguous()
+    K.swiglu(planes, h, 64)
+    assert _rel(h.float(), ref) < 1.5e-2

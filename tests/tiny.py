@@ -24,7 +24,7 @@ TINY_C = dict(architectures=["NanbeigeForCausalLM"], model_type="llama", vocab_s
 # D and E have the head sizes the tensor-core attention kernels take (64, 128) with 5 and 3 query heads per key/value
 # head, so the bfloat16 runs of these two go through the serving kernels end to end
 TINY_D = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=500, hidden_size=160,
-              intermediate_size=264, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=1, head_dim=64,
+              intermediate_size=320, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=1, head_dim=64,
               rms_norm_eps=1e-5, rope_theta=70000000.0, tie_word_embeddings=False)
 TINY_E = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=777, hidden_size=200,
               intermediate_size=344, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
