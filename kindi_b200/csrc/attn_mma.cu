@@ -43,7 +43,7 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
 }
 
 template <int HD, bool DEC>
-__global__ void __launch_bounds__(AT_THREADS) k_attn_mma(const __grid_constant__ CUtensorMap kvmap,
+__global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constant__ CUtensorMap kvmap,
         const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
         float* __restrict__ part_ml, const int* __restrict__ slot, const int* __restrict__ q_start,
         const int* __restrict__ kv_len, int nh, int nkv, int G, float scale_log2e, int window,
@@ -369,6 +369,9 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        if (e != cudaSuccess) return (int)e;
+        // two CTAs are meant to share an SM: ask for the largest shared-memory carve-out
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }

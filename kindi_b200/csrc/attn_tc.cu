@@ -1,0 +1,324 @@
+// Prefill attention on the 5th-generation tensor cores: S = Q K^T and O += P V are tcgen05.mma instructions with their
+// accumulators in tensor memory; softmax runs in 32-bit on the CUDA cores between them.
+//
+// One CTA serves one key/value head of one sequence and up to 128 rows r = token * G + j (token of this step, query
+// head j of the group: the reference packs rows the same way, kindi/nbq_fa.cu:3-5,40-49), TOK = 128 / G whole tokens.
+// Warps 0-3 (one thread per row) do the softmax, warp 4 brings pages of 64 positions in by TMA (two 64-column tile
+// loads per 128-wide head for K and for V, 128-byte swizzle, no multicast), one thread of warp 5 issues the MMAs:
+//     S[j % 2] = Q K_j^T      M 128 x N 64 x K 128: Q and K both K-major in shared memory
+//     O       += P_j V_j      M 128 x N 128 x K 64: P K-major (written by the softmax threads), V as stored in the cache,
+//                              i.e. MN-major
+// S has two buffers in tensor memory so that Q K^T of the next page runs while the softmax of this one does; P has two
+// buffers in shared memory. The running maximum is applied lazily: the exponent's reference only moves (and O in tensor
+// memory is only rescaled, by tcgen05.ld / tcgen05.st) when a row's maximum has grown by more than 8 (a factor 256 in
+// the probabilities, which bf16 and the 32-bit sums hold without loss); the final division by the row sum makes the
+// result the same as with an exact running maximum (kindi/nbq_fa.cu:31-151 is the recurrence this follows).
+// Head size 128. Every wait is bounded (sm100.cuh); all tcgen05 loads and stores are executed by whole warps.
+#include "sm100.cuh"
+
+#define FT_THREADS 192
+#define FT_STAGES 3
+#define FT_HD 128
+#define FT_TILE_BYTES (64 * FT_HD * 2)           // one page of keys (or values) of one head: 16 KB
+#define FT_STAGE_BYTES (2 * FT_TILE_BYTES)
+#define FT_Q_BYTES (128 * FT_HD * 2)             // 32 KB: two K-blocks of [128 rows][64 columns]
+#define FT_P_BYTES (128 * 64 * 2)                // 16 KB
+#define FT_LAZY 8.0f
+
+__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) { tmem_ld_32x32(taddr, r); }
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// shared-memory descriptor of an MN-major operand tile stored as rows of 128 bytes (64 elements of the MN dimension per
+// row, one row per K index), 128-byte swizzle: leading byte offset = distance to the next block of 64 MN elements,
+// stride byte offset = distance between groups of 8 K rows (1024)
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(FT_THREADS) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
+        const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
+        const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
+        const int* __restrict__ table, int table_stride, int n_pages, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    kb_pdl_launch();
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t s_q = sbase, s_kv = s_q + FT_Q_BYTES, s_p = s_kv + FT_STAGES * FT_STAGE_BYTES;
+    const uint32_t bars = s_p + 2 * FT_P_BYTES;
+    const uint32_t b_kv_full = bars, b_kv_empty = b_kv_full + FT_STAGES * 8, b_s_full = b_kv_empty + FT_STAGES * 8;
+    const uint32_t b_s_free = b_s_full + 16, b_p_ready = b_s_free + 16, b_p_free = b_p_ready + 16;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + 2 * FT_P_BYTES +
+                                                        (2 * FT_STAGES + 8) * 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, hk = blockIdx.y;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < FT_STAGES; s++) {
+            mbar_init(b_kv_full + s * 8, 1);
+            mbar_init(b_kv_empty + s * 8, 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(b_s_full + i * 8, 1);
+            mbar_init(b_s_free + i * 8, 4);
+            mbar_init(b_p_ready + i * 8, 4);
+            mbar_init(b_p_free + i * 8, 1);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&kvmap);
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), 256);
+        tmem_relinquish();
+    }
+    kb_pdl_wait();                       // the step's metadata, Q and the newest keys come from earlier kernels
+    const int qs0 = q_start[b], qlen = q_start[b + 1] - qs0, kvl = kv_len[b];
+    const int pos0 = kvl - qlen;
+    const int TOK = 128 / G;                         // whole tokens per CTA
+    const int n_tiles = (qlen + TOK - 1) / TOK;
+    const bool active = (int)blockIdx.x < n_tiles;   // uniform over the CTA
+    const int tile = n_tiles - 1 - (int)blockIdx.x;  // the longest tiles first
+    const int tok0 = tile * TOK;
+    const int ntok = active ? min(TOK, qlen - tok0) : 0;
+    const int nrows = ntok * G;
+    // pages this CTA reads
+    const int p_first = pos0 + tok0, p_last = pos0 + tok0 + ntok - 1;
+    const int lo_cta = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    const int pg_lo = lo_cta / KB_PAGE, pg_hi = p_last / KB_PAGE;
+    const int n_iter = active ? pg_hi - pg_lo + 1 : 0;
+
+    // ---- Q into shared memory: two K-blocks of [128 rows][64 columns], rows of 128 bytes, 128-byte swizzle
+    if (active) {
+        for (int e = threadIdx.x; e < 128 * 16; e += FT_THREADS) {
+            const int r = e >> 4, c = e & 15;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < nrows) v = *(const uint4*)(q + (size_t)(qs0 + tok0 + r / G) * ldq + (size_t)(hk * G + r % G) * FT_HD + c * 8);
+            *(uint4*)(smem + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t t_s = tmem, t_o = tmem + 128;     // S buffers at columns 0 and 64, O at 128..255
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0 && n_iter > 0) {
+            const int* trow = table + (size_t)slot[b] * table_stride;
+            for (int i = 0; i < n_iter; i++) {
+                const int s = i % FT_STAGES;
+                const uint32_t ph = (uint32_t)(i / FT_STAGES) & 1u;
+                if (!mbar_wait(b_kv_empty + s * 8, ph ^ 1u, status)) break;
+                int page = trow[pg_lo + i];
+                if (page < 0 || page >= n_pages) {
+                    atomicOr(status, KB_ST_BAD_PAGE);
+                    page = 0;
+                }
+                mbar_expect_tx(b_kv_full + s * 8, FT_STAGE_BYTES);
+                const uint32_t dst = s_kv + s * FT_STAGE_BYTES;
+                const int krow = ((page * 2 + 0) * nkv + hk) * KB_PAGE, vrow = ((page * 2 + 1) * nkv + hk) * KB_PAGE;
+                tma_load_2d(dst, &kvmap, 0, krow, b_kv_full + s * 8);
+                tma_load_2d(dst + 8192, &kvmap, 64, krow, b_kv_full + s * 8);
+                tma_load_2d(dst + FT_TILE_BYTES, &kvmap, 0, vrow, b_kv_full + s * 8);
+                tma_load_2d(dst + FT_TILE_BYTES + 8192, &kvmap, 64, vrow, b_kv_full + s * 8);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_iter > 0) {
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64);                  // Q K^T: both K-major
+            constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);    // P V: V is MN-major
+            bool ok = true;
+            auto issue_s = [&](int j) {
+                const int s = j % FT_STAGES;
+                const uint32_t kt = s_kv + s * FT_STAGE_BYTES;
+                const uint32_t d = t_s + (uint32_t)(j & 1) * 64;
+#pragma unroll
+                for (int k = 0; k < 8; k++)          // 128 columns of the head = 2 blocks of 64 = 8 steps of 16
+                    umma_bf16(d, umma_desc_sw128(s_q + (k >> 2) * 16384 + (k & 3) * 32),
+                              umma_desc_sw128(kt + (k >> 2) * 8192 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(b_s_full + (j & 1) * 8);
+            };
+            ok = mbar_wait(b_kv_full, 0, status);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; j < n_iter && ok; j++) {
+                if (j + 1 < n_iter) {
+                    const int s1 = (j + 1) % FT_STAGES;
+                    if (!(ok = mbar_wait(b_kv_full + s1 * 8, (uint32_t)((j + 1) / FT_STAGES) & 1u, status))) break;
+                    // S buffer (j + 1) & 1 was last read for page j - 1
+                    if (j >= 1 && !(ok = mbar_wait(b_s_free + ((j + 1) & 1) * 8, (uint32_t)((j - 1) >> 1) & 1u, status))) break;
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                if (!(ok = mbar_wait(b_p_ready + (j & 1) * 8, (uint32_t)(j >> 1) & 1u, status))) break;
+                tc_fence_after();
+                const uint32_t pt = s_p + (uint32_t)(j & 1) * FT_P_BYTES;
+                const uint32_t vt = s_kv + (j % FT_STAGES) * FT_STAGE_BYTES + FT_TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < 4; k++)          // 64 keys = 4 steps of 16
+                    umma_bf16(t_o, umma_desc_sw128(pt + k * 32), umma_desc_mn_sw128(vt + k * 2048, 8192), idesc_o,
+                              (j > 0 || k > 0) ? 1u : 0u);
+                umma_commit(b_p_free + (j & 1) * 8);              // P buffer free; O holds pages 0..j
+                umma_commit(b_kv_empty + (j % FT_STAGES) * 8);    // the stage's K and V have been read
+            }
+        }
+    } else if (n_iter > 0) {
+        // ------------------------------------------------------------ softmax: thread = row = TMEM lane
+        const int r = warp * 32 + lane;
+        const bool row_ok = r < nrows;
+        const int p_row = row_ok ? pos0 + tok0 + r / G : -1;
+        const int lo_row = (window > 0 && p_row - window + 1 > 0) ? p_row - window + 1 : 0;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_iter && ok; j++) {
+            const int bsel = j & 1;
+            if (!(ok = mbar_wait(b_s_full + bsel * 8, (uint32_t)(j >> 1) & 1u, status))) break;
+            __syncwarp();
+            tc_fence_after();
+            uint32_t sv[64];
+            tmem_ld_x32(t_s + lane_base + bsel * 64, sv);
+            tmem_ld_x32(t_s + lane_base + bsel * 64 + 32, sv + 32);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_s_free + bsel * 8);
+            // scale, mask, row maximum
+            const int key0 = (pg_lo + j) * KB_PAGE;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; c++) {
+                const int p = key0 + c;
+                const float s = (p <= p_row && p >= lo_row) ? __uint_as_float(sv[c]) * scale_log2e : -INFINITY;
+                sv[c] = __float_as_uint(s);
+                mx = fmaxf(mx, s);
+            }
+            // lazy reference: move it only when the maximum has grown by more than FT_LAZY
+            const bool grow = mx > m_ref + FT_LAZY || (m_ref == -INFINITY && mx > -INFINITY);
+            float f = 1.0f;
+            if (grow) {
+                f = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - mx);
+                m_ref = mx;
+                l *= f;
+            }
+            if (__any_sync(0xffffffffu, grow) && j > 0) {
+                // O holds pages 0..j-1 once their MMAs are done
+                if (!(ok = mbar_wait(b_p_free + ((j - 1) & 1) * 8, (uint32_t)((j - 1) >> 1) & 1u, status))) break;
+                __syncwarp();
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld_x32(t_o + lane_base + c0, ov);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; c++) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * f);
+                    tmem_st_x32(t_o + lane_base + c0, ov);
+                }
+                tmem_st_wait();
+            }
+            // probabilities (relative to the reference), their sum, and P as bf16 into shared memory
+            const float mr = m_ref == -INFINITY ? 0.0f : m_ref;
+            // P buffer bsel was last read by the MMAs of page j - 2
+            if (j >= 2 && !(ok = mbar_wait(b_p_free + bsel * 8, (uint32_t)((j - 2) >> 1) & 1u, status))) break;
+            uint8_t* prow = smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + bsel * FT_P_BYTES + r * 128;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; c8++) {
+                uint32_t h[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const float p0 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * c]) - mr);
+                    const float p1 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * c + 1]) - mr);
+                    sum += p0 + p1;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                    h[c] = *(uint32_t*)&v;
+                }
+                *(uint4*)(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+            l += sum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_p_ready + bsel * 8);
+        }
+        // ---- O / l once the last P V is done
+        if (ok) ok = mbar_wait(b_p_free + ((n_iter - 1) & 1) * 8, (uint32_t)((n_iter - 1) >> 1) & 1u, status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            bf16* dst = out + (size_t)(qs0 + tok0 + (row_ok ? r / G : 0)) * ldo + (size_t)(hk * G + (row_ok ? r % G : 0)) * FT_HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld_x32(t_o + lane_base + c0, ov);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(ov[c + 2 * k]) * inv,
+                                                                     __uint_as_float(ov[c + 2 * k + 1]) * inv);
+                            h[k] = *(uint32_t*)&v;
+                        }
+                        *(uint4*)(dst + c0 + c) = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 256);
+    }
+}
+
+// grid_x = the most tiles of a sequence: ceil(longest q_len / (128 / G)) with G = nh / nkv <= 128
+extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int* slot, const int* q_start,
+                          const int* kv_len, int B, int nh, int nkv, int hd, float scale, int window, void* pool,
+                          const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st) {
+    if (B <= 0 || grid_x <= 0) return 0;
+    if (hd != FT_HD || nkv <= 0 || nh % nkv || nh / nkv > 128) return (int)cudaErrorInvalidValue;
+    if ((ldq % 8) || (ldo % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map;
+    int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
+    if (rc) return rc;
+    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + 2 * FT_P_BYTES + (2 * FT_STAGES + 8) * 8 + 16 + 1024;
+    static bool done = false;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(k_attn_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    dim3 grid(grid_x, nkv, B);
+    cudaError_t e = kb_launch(k_attn_tc, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot, q_start,
+                              kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table, table_stride, n_pages,
+                              status);
+    return (int)e;
+}

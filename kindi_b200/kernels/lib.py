@@ -44,6 +44,8 @@ _SIGS = {
     "kb_gemm_tc_splits": [c_int, c_int],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "kb_attn_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_sample": [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
                   c_void_p],
     "kb_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_float, c_void_p],
@@ -261,3 +263,16 @@ def attn_mma(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, 
            "attn_mma")
     if decode and grid_x > 1:
         add_launches(1)         # the merge of the position splits
+
+
+def attn_tc(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
+            scale: float, window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, grid_x: int,
+            status: torch.Tensor) -> None:
+    """tcgen05 attention for prompt-sized steps (bf16, head size 128): grid_x = ceil(most rows of a sequence /
+    (128 // (nh / nkv)))"""
+    _need_cuda(q, out, pool, table)
+    assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert pool.is_contiguous() and hd == 128
+    _check(load().kb_attn_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(slot), _p(q_start), _p(kv_len), B, nh, nkv,
+                             hd, float(scale), int(window), _p(pool), _p(table), table.stride(0), n_pages, grid_x,
+                             _p(status), _stream()), "attn_tc")

@@ -136,6 +136,10 @@ def _run_attention(K, kind, dtype, nh, nkv, hd, q_lens, kv_lens, window, seed, b
     st = _status()
     if kind == "generic":
         K.attn_generic(qd, out, dev(pos), dev(seq), slots, nh, nkv, hd, scale, window, pool, table, n_pages, st)
+    elif kind == "tc":
+        G = nh // nkv
+        K.attn_tc(qd, out, slots, dev(q_start), dev(kv_lens), len(q_lens), nh, nkv, hd, scale, window, pool, table,
+                  n_pages, grid_x=-(-max(q_lens) // (128 // G)), status=st)
     else:
         G = nh // nkv
         gx = 5 if kind == "decode" else -(-max(q_lens) * G // 64)
@@ -208,3 +212,18 @@ def test_gemm_tc_finishes_swiglu_in_its_epilogue(K, M, F, K_, bn):
     planes = rows.float()[None].contiguous()
     K.swiglu(planes, h, 64)
     assert _rel(h.float(), ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("nh,nkv,window", [(20, 4, 0), (3, 1, 0), (8, 8, 0), (10, 2, 64), (16, 1, 0), (6, 2, 100)])
+def test_attention_tc_prefill(K, nh, nkv, window):
+    # whole prompts, a chunk that continues an earlier part, single rows, lengths at and around page edges
+    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, 128, [64, 1, 130, 33, 7], [64, 129, 130, 97, 200],
+                         window, seed=nh)
+    assert err < 1e-2
+    # one far key among hundreds decides a row (the lazy maximum has to follow it)
+    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, 128, [40, 3], [700, 65], window=0, seed=nh + 1,
+                         boost=(0, 39, 5))
+    assert err < 1e-2
+    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, 128, [300], [300], window=window, seed=nh + 2,
+                         boost=(0, 299, 250))
+    assert err < 1e-2
