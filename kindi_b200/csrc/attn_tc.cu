@@ -8,8 +8,9 @@
 //     S[j % 2] = Q K_j^T      M 128 x N 64 x K 128: Q and K both K-major in shared memory
 //     O       += P_j V_j      M 128 x N 128 x K 64: P K-major (written by the softmax threads), V as stored in the cache,
 //                              i.e. MN-major
-// S has two buffers in tensor memory so that Q K^T of the next page runs while the softmax of this one does; P has two
-// buffers in shared memory. The running maximum is applied lazily: the exponent's reference only moves (and O in tensor
+// S has two buffers in tensor memory so that Q K^T of the next page runs while the softmax of this one does; P has one
+// buffer in shared memory (P V of a page is long done when the next page's probabilities are ready). A CTA needs 112 KB
+// of shared memory and 256 columns of tensor memory, so two CTAs share an SM and one's softmax hides the other's waits. The running maximum is applied lazily: the exponent's reference only moves (and O in tensor
 // memory is only rescaled, by tcgen05.ld / tcgen05.st) when a row's maximum has grown by more than 8 (a factor 256 in
 // the probabilities, which bf16 and the 32-bit sums hold without loss); the final division by the row sum makes the
 // result the same as with an exact running maximum (kindi/nbq_fa.cu:31-151 is the recurrence this follows).
@@ -17,7 +18,7 @@
 #include "sm100.cuh"
 
 #define FT_THREADS 192
-#define FT_STAGES 3
+#define FT_STAGES 2
 #define FT_HD 128
 #define FT_TILE_BYTES (64 * FT_HD * 2)           // one page of keys (or values) of one head: 16 KB
 #define FT_STAGE_BYTES (2 * FT_TILE_BYTES)
@@ -37,6 +38,11 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t* r) {
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ float ft_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // shared-memory descriptor of an MN-major operand tile stored as rows of 128 bytes (64 elements of the MN dimension per
@@ -52,20 +58,20 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
     return d;
 }
 
-__global__ void __launch_bounds__(FT_THREADS) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
+__global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
         const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
         const int* __restrict__ table, int table_stride, int n_pages, int* status) {
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     kb_pdl_launch();
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t s_q = sbase, s_kv = s_q + FT_Q_BYTES, s_p = s_kv + FT_STAGES * FT_STAGE_BYTES;
-    const uint32_t bars = s_p + 2 * FT_P_BYTES;
+    const uint32_t bars = s_p + FT_P_BYTES;
     const uint32_t b_kv_full = bars, b_kv_empty = b_kv_full + FT_STAGES * 8, b_s_full = b_kv_empty + FT_STAGES * 8;
-    const uint32_t b_s_free = b_s_full + 16, b_p_ready = b_s_free + 16, b_p_free = b_p_ready + 16;
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + 2 * FT_P_BYTES +
-                                                        (2 * FT_STAGES + 8) * 8);
+    const uint32_t b_s_free = b_s_full + 16, b_p_ready = b_s_free + 16, b_p_free = b_p_ready + 8;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + FT_P_BYTES +
+                                                        (2 * FT_STAGES + 6) * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, hk = blockIdx.y;
 
@@ -77,9 +83,9 @@ __global__ void __launch_bounds__(FT_THREADS) k_attn_tc(const __grid_constant__ 
         for (int i = 0; i < 2; i++) {
             mbar_init(b_s_full + i * 8, 1);
             mbar_init(b_s_free + i * 8, 4);
-            mbar_init(b_p_ready + i * 8, 4);
-            mbar_init(b_p_free + i * 8, 1);
         }
+        mbar_init(b_p_ready, 4);
+        mbar_init(b_p_free, 1);
         mbar_fence_init();
         tma_prefetch_desc(&kvmap);
     }
@@ -171,15 +177,15 @@ __global__ void __launch_bounds__(FT_THREADS) k_attn_tc(const __grid_constant__ 
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                if (!(ok = mbar_wait(b_p_ready + (j & 1) * 8, (uint32_t)(j >> 1) & 1u, status))) break;
+                if (!(ok = mbar_wait(b_p_ready, (uint32_t)j & 1u, status))) break;
                 tc_fence_after();
-                const uint32_t pt = s_p + (uint32_t)(j & 1) * FT_P_BYTES;
+                const uint32_t pt = s_p;
                 const uint32_t vt = s_kv + (j % FT_STAGES) * FT_STAGE_BYTES + FT_TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < 4; k++)          // 64 keys = 4 steps of 16
                     umma_bf16(t_o, umma_desc_sw128(pt + k * 32), umma_desc_mn_sw128(vt + k * 2048, 8192), idesc_o,
                               (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(b_p_free + (j & 1) * 8);              // P buffer free; O holds pages 0..j
+                umma_commit(b_p_free);                            // P buffer free; O holds pages 0..j
                 umma_commit(b_kv_empty + (j % FT_STAGES) * 8);    // the stage's K and V have been read
             }
         }
@@ -206,27 +212,41 @@ __global__ void __launch_bounds__(FT_THREADS) k_attn_tc(const __grid_constant__ 
             if (lane == 0) mbar_arrive(b_s_free + bsel * 8);
             // scale, mask, row maximum
             const int key0 = (pg_lo + j) * KB_PAGE;
-            float mx = -INFINITY;
+            // four independent running maxima (one long dependent chain would leave the few resident warps idle)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (key0 + 63 <= p_row && key0 >= lo_row) {
+                // the whole page lies inside this row's span (all pages but the last one or two): no masks
 #pragma unroll
-            for (int c = 0; c < 64; c++) {
-                const int p = key0 + c;
-                const float s = (p <= p_row && p >= lo_row) ? __uint_as_float(sv[c]) * scale_log2e : -INFINITY;
-                sv[c] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int c = 0; c < 64; c++) {
+                    const float s = __uint_as_float(sv[c]) * scale_log2e;
+                    sv[c] = __float_as_uint(s);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], s);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 64; c++) {
+                    const int p = key0 + c;
+                    const float s = (p <= p_row && p >= lo_row) ? __uint_as_float(sv[c]) * scale_log2e : -INFINITY;
+                    sv[c] = __float_as_uint(s);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], s);
+                }
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // lazy reference: move it only when the maximum has grown by more than FT_LAZY
             const bool grow = mx > m_ref + FT_LAZY || (m_ref == -INFINITY && mx > -INFINITY);
             float f = 1.0f;
             if (grow) {
-                f = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - mx);
+                f = m_ref == -INFINITY ? 0.0f : ft_exp2(m_ref - mx);
                 m_ref = mx;
                 l *= f;
             }
-            if (__any_sync(0xffffffffu, grow) && j > 0) {
-                // O holds pages 0..j-1 once their MMAs are done
-                if (!(ok = mbar_wait(b_p_free + ((j - 1) & 1) * 8, (uint32_t)((j - 1) >> 1) & 1u, status))) break;
+            // P V of page j - 1 is done: O holds pages 0..j-1 and the P buffer is free
+            if (j > 0) {
+                if (!(ok = mbar_wait(b_p_free, (uint32_t)(j - 1) & 1u, status))) break;
                 __syncwarp();
                 tc_fence_after();
+            }
+            if (__any_sync(0xffffffffu, grow) && j > 0) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < 128; c0 += 32) {
                     uint32_t ov[32];
@@ -240,31 +260,29 @@ __global__ void __launch_bounds__(FT_THREADS) k_attn_tc(const __grid_constant__ 
             }
             // probabilities (relative to the reference), their sum, and P as bf16 into shared memory
             const float mr = m_ref == -INFINITY ? 0.0f : m_ref;
-            // P buffer bsel was last read by the MMAs of page j - 2
-            if (j >= 2 && !(ok = mbar_wait(b_p_free + bsel * 8, (uint32_t)((j - 2) >> 1) & 1u, status))) break;
-            uint8_t* prow = smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + bsel * FT_P_BYTES + r * 128;
-            float sum = 0.0f;
+            uint8_t* prow = smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + r * 128;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) {
                 uint32_t h[4];
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    const float p0 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * c]) - mr);
-                    const float p1 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * c + 1]) - mr);
-                    sum += p0 + p1;
+                    const float p0 = ft_exp2(__uint_as_float(sv[c8 * 8 + 2 * c]) - mr);
+                    const float p1 = ft_exp2(__uint_as_float(sv[c8 * 8 + 2 * c + 1]) - mr);
+                    sum4[c] += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                     h[c] = *(uint32_t*)&v;
                 }
                 *(uint4*)(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(b_p_ready + bsel * 8);
+            if (lane == 0) mbar_arrive(b_p_ready);
         }
         // ---- O / l once the last P V is done
-        if (ok) ok = mbar_wait(b_p_free + ((n_iter - 1) & 1) * 8, (uint32_t)((n_iter - 1) >> 1) & 1u, status);
+        if (ok) ok = mbar_wait(b_p_free, (uint32_t)(n_iter - 1) & 1u, status);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after();
@@ -309,10 +327,13 @@ extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int*
     CUtensorMap map;
     int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
     if (rc) return rc;
-    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + 2 * FT_P_BYTES + (2 * FT_STAGES + 8) * 8 + 16 + 1024;
+    // 112 KB of tiles + barriers + what aligning the base to 1024 can cost when it is aligned to 128: two CTAs fit
+    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + FT_P_BYTES + 128 + 896;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(k_attn_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(k_attn_tc, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }

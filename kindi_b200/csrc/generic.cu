@@ -130,6 +130,43 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict_
         yr[i] = kb_from_f<TY>(__fmul_rn(__fmul_rn(scale, sv[i]), kb_to_f<TW>(w[i])));
 }
 
+// The same operation with one warp per row, for prompt-sized steps of the bf16 path: no shared memory and no block
+// barrier; the row is read twice (the second time from the cache, it has just been written). The sum of squares is
+// taken in another order than in k_add_rmsnorm, so the true 32-bit path, whose results must not depend on how many rows
+// a step has, never uses it.
+template <typename TW>
+__global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* __restrict__ x, const float* __restrict__ delta,
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float* xr = x + (size_t)t * E;
+    const float* dr = delta + (size_t)t * E;
+    float ss = 0.0f;
+    for (int i = lane * 4; i < E; i += 128) {
+        float4 v = *(const float4*)(xr + i);
+        if (n_delta > 0) {
+            v = kb_sum_planes4(v, dr + i, n_delta, delta_stride);
+            *(float4*)(xr + i) = v;
+        }
+        ss = fmaf(v.x, v.x, ss);
+        ss = fmaf(v.y, v.y, ss);
+        ss = fmaf(v.z, v.z, ss);
+        ss = fmaf(v.w, v.w, ss);
+    }
+    ss = kb_warp_sum(ss);
+    const float scale = rsqrtf(ss / (float)E + eps);
+    bf16* yr = y + (size_t)t * E;
+    for (int i = lane * 4; i < E; i += 128) {
+        const float4 v = *(const float4*)(xr + i);
+        const float w0 = kb_to_f<TW>(w[i]), w1 = kb_to_f<TW>(w[i + 1]), w2 = kb_to_f<TW>(w[i + 2]), w3 = kb_to_f<TW>(w[i + 3]);
+        __nv_bfloat162 a = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(scale, v.x), w0), __fmul_rn(__fmul_rn(scale, v.y), w1));
+        __nv_bfloat162 b = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(scale, v.z), w2), __fmul_rn(__fmul_rn(scale, v.w), w3));
+        *(uint2*)(yr + i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    }
+}
+
 extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long long delta_stride, const void* w,
                               int wdtype, float eps, void* y, int ydtype, const int* rows, int n_out, int T, int E,
                               int write_back, int* status, cudaStream_t st) {
@@ -139,6 +176,16 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
     const bool vec = (E % 4 == 0) && (((uintptr_t)x) % 16 == 0) && (((uintptr_t)delta) % 16 == 0) &&
                      (delta_stride % 4 == 0);
     cudaError_t e = cudaSuccess;
+    if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= 512 && (write_back || n_delta == 0) &&
+        (((uintptr_t)y) % 8) == 0) {
+        if (wdtype == KB_F32)
+            e = kb_launch(k_add_rmsnorm_warp<float>, (T + 7) / 8, 256, 0, st, x, delta, n_delta, (size_t)delta_stride,
+                          (const float*)w, eps, (bf16*)y, T, E);
+        else
+            e = kb_launch(k_add_rmsnorm_warp<bf16>, (T + 7) / 8, 256, 0, st, x, delta, n_delta, (size_t)delta_stride,
+                          (const bf16*)w, eps, (bf16*)y, T, E);
+        return (int)e;
+    }
 #define KB_NORM1(TY, TW, V)                                                                                      \
     do {                                                                                                         \
         if (sm > 48 * 1024)                                                                                      \
