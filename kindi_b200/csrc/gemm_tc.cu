@@ -19,9 +19,9 @@
 #define TC_BK 64
 #define TC_THREADS 192          // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT = 1>
 struct TcSmem {
-    static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+    static constexpr int A_BYTES = MT * TC_BM * TC_BK * 2;
     static constexpr int B_BYTES = BN * TC_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
@@ -29,11 +29,15 @@ struct TcSmem {
     static constexpr int TOTAL = BAR_OFF + N_BARS * 8 + 16 + 1024;     // + alignment slack
 };
 
-template <int BN, int STAGES, bool SWAP, typename TC>
+// MT = 2 (prefill form only): a unit is TWO 128-row tiles of the same BN columns, so one weight tile in shared memory
+// feeds two accumulators: less traffic from the L2 per FLOP, at the price of not overlapping the epilogue with the next
+// unit (both accumulators are in use).
+template <int BN, int STAGES, bool SWAP, typename TC, int MT = 1>
 __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ CUtensorMap mapP,
         const __grid_constant__ CUtensorMap mapQ, TC* __restrict__ C, int rowsP, int rowsQ, int K, int ldc,
         long long split_stride, int kb_per_split, int n_splits, int* status, int swiglu_ld) {
-    using S = TcSmem<BN, STAGES>;
+    using S = TcSmem<BN, STAGES, MT>;
+    static_assert(MT == 1 || (!SWAP && 2 * BN <= 512), "two row tiles: prefill form, both accumulators in tensor memory");
     extern __shared__ uint8_t smem_raw[];
     kb_pdl_launch();
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -42,10 +46,11 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
     const uint32_t bar_acc_full = bar_empty + STAGES * 8, bar_acc_empty = bar_acc_full + 16;
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + S::BAR_OFF + S::N_BARS * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tilesP = (rowsP + TC_BM - 1) / TC_BM, tilesQ = (rowsQ + BN - 1) / BN;
+    const int tilesP = (rowsP + MT * TC_BM - 1) / (MT * TC_BM), tilesQ = (rowsQ + BN - 1) / BN;
     const int n_units = tilesP * tilesQ * n_splits;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     // two accumulators: the second starts at half of the allocation (a power of two of at least 2 x BN columns)
+    // (MT == 2: the two halves are the two row tiles' accumulators, and there is no second buffer)
     constexpr uint32_t TMEM_COLS = BN <= 16 ? 32 : BN <= 32 ? 64 : BN <= 64 ? 128 : BN <= 128 ? 256 : 512;
     constexpr uint32_t ACC_COLS = TMEM_COLS / 2;
 
@@ -97,7 +102,10 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                     if (!(ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, status))) break;
                     mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
                     const uint32_t dst = sbase + s * S::STAGE_BYTES;
-                    tma_load_2d(dst, &mapP, kb * TC_BK, tp * TC_BM, bar_full + s * 8);
+#pragma unroll
+                    for (int m = 0; m < MT; m++)
+                        tma_load_2d(dst + m * (TC_BM * TC_BK * 2), &mapP, kb * TC_BK, (tp * MT + m) * TC_BM,
+                                    bar_full + s * 8);
                     if (waited) {
                         tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
                     } else {
@@ -122,8 +130,9 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, it++) {
                 const int sp = (u / tilesP) / tilesQ;
                 const int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
-                const uint32_t acc = it & 1u;
-                if (!(ok = mbar_wait(bar_acc_empty + acc * 8, ((it >> 1) & 1u) ^ 1u, status))) break;
+                const uint32_t acc = MT == 2 ? 0u : (it & 1u);
+                const uint32_t acc_ph = MT == 2 ? (it & 1u) : ((it >> 1) & 1u);
+                if (!(ok = mbar_wait(bar_acc_empty + acc * 8, acc_ph ^ 1u, status))) break;
                 tc_fence_after();
                 const uint32_t d = tmem + acc * ACC_COLS;
                 for (int kb = kb0; kb < kb1; kb++, n++) {
@@ -134,8 +143,10 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                     const uint32_t a = sbase + s * S::STAGE_BYTES, b = a + S::A_BYTES;
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; k++)
-                        umma_bf16(d, umma_desc_sw128(a + k * 32), umma_desc_sw128(b + k * 32), idesc,
-                                  (kb > kb0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int m = 0; m < MT; m++)
+                            umma_bf16(d + m * ACC_COLS, umma_desc_sw128(a + m * (TC_BM * TC_BK * 2) + k * 32),
+                                      umma_desc_sw128(b + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit(bar_empty + s * 8);
                 }
                 umma_commit(bar_acc_full + acc * 8);
@@ -149,13 +160,17 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         kb_pdl_wait();                                   // C may be memory that an earlier kernel still reads
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, it++) {
             const int tp = u % tilesP, rest = u / tilesP, tq = rest % tilesQ, sp = rest / tilesQ;
-            const int p0 = tp * TC_BM, q0 = tq * BN;
-            const uint32_t acc = it & 1u;
-            if (!(ok = mbar_wait(bar_acc_full + acc * 8, (it >> 1) & 1u, status))) break;
+            const int q0 = tq * BN;
+            const uint32_t acc = MT == 2 ? 0u : (it & 1u);
+            const uint32_t acc_ph = MT == 2 ? (it & 1u) : ((it >> 1) & 1u);
+            if (!(ok = mbar_wait(bar_acc_full + acc * 8, acc_ph, status))) break;
             tc_fence_after();
-            const int prow = p0 + quarter * 32 + lane;           // row of the 128-row side this thread holds
             TC* Cz = C + (size_t)sp * split_stride;
-            const uint32_t tbase = tmem + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int mt = 0; mt < MT; mt++) {
+            const int p0 = (tp * MT + mt) * TC_BM;
+            const int prow = p0 + quarter * 32 + lane;           // row of the 128-row side this thread holds
+            const uint32_t tbase = tmem + (acc + mt) * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             if (!SWAP && BN % 128 == 0 && swiglu_ld > 0) {
                 // the weights' rows come in groups of 64 gate rows followed by the 64 up rows of the same outputs, so
                 // a tile holds both halves of BN / 2 outputs: out[token][j] = silu(gate) * up goes out as bf16 and the
@@ -226,7 +241,8 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                     }
                 }
             }
-            // this warp has read its lanes of the accumulator: hand it back to the MMA thread
+            }
+            // this warp has read its lanes of the accumulator(s): hand them back to the MMA thread
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_empty + acc * 8);
@@ -250,11 +266,11 @@ static int kb_sm_count() {
     return n;
 }
 
-template <int BN, int STAGES, bool SWAP, typename TC>
+template <int BN, int STAGES, bool SWAP, typename TC, int MT = 1>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int rowsP, int rowsQ, int K, int ldc,
                      int splits, long long split_stride, int* status, cudaStream_t st, int swiglu_ld) {
-    using S = TcSmem<BN, STAGES>;
-    auto kern = k_gemm_tc<BN, STAGES, SWAP, TC>;
+    using S = TcSmem<BN, STAGES, MT>;
+    auto kern = k_gemm_tc<BN, STAGES, SWAP, TC, MT>;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -264,7 +280,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     int kbps = (total_kb + splits - 1) / splits;
     int z = (total_kb + kbps - 1) / kbps;               // every split has at least one k-block
-    const int units = ((rowsP + TC_BM - 1) / TC_BM) * ((rowsQ + BN - 1) / BN) * z;
+    const int units = ((rowsP + MT * TC_BM - 1) / (MT * TC_BM)) * ((rowsQ + BN - 1) / BN) * z;
     const int grid = units < kb_sm_count() ? units : kb_sm_count();
     if (swiglu_ld > 0 && (SWAP || BN % 128 || sizeof(TC) != 2 || z != 1)) return (int)cudaErrorInvalidValue;
     kb_launch(kern, grid, TC_THREADS, S::TOTAL, st, mp, mq, (TC*)C, rowsP, rowsQ, K, ldc, split_stride, kbps, z, status,
@@ -287,7 +303,8 @@ extern "C" int kb_gemm_tc_splits(int K, int wanted) {
 // bf16 [M][N / 2] result silu(gate) * up with row stride ldc.
 extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int M, int N, int K, int lda, int ldw,
                           int ldc, int swap, int bn, int splits, long long split_stride, int* status,
-                          cudaStream_t st, int swiglu = 0) {
+                          cudaStream_t st, int swiglu = 0, int mt = 1) {
+    if (mt != 1 && (mt != 2 || swap || splits != 1)) return (int)cudaErrorInvalidValue;
     if (swiglu && (swap || (N % 128) || cdtype != KB_BF16 || splits != 1 || (ldc % 8) || ((uintptr_t)C & 15)))
         return (int)cudaErrorInvalidValue;
     const int swiglu_ld = swiglu ? ldc : 0;
@@ -314,6 +331,20 @@ extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int
             case 128: TC_GO(128, 5, true);
             default: return (int)cudaErrorInvalidValue;
         }
+    } else if (mt == 2) {
+#define TC_GO2(BN, ST)                                                                                               \
+    return cdtype == KB_F32                                                                                          \
+               ? launch_tc<BN, ST, false, float, 2>(mp, mq, C, rowsP, rowsQ, K, ldc, splits, split_stride, status, st, swiglu_ld) \
+               : launch_tc<BN, ST, false, bf16, 2>(mp, mq, C, rowsP, rowsQ, K, ldc, splits, split_stride, status, st, swiglu_ld)
+        switch (bn) {
+            case 128: TC_GO2(128, 4);
+            case 160: TC_GO2(160, 4);
+            case 192: TC_GO2(192, 3);
+            case 224: TC_GO2(224, 3);
+            case 256: TC_GO2(256, 3);
+            default: return (int)cudaErrorInvalidValue;
+        }
+#undef TC_GO2
     } else {
         switch (bn) {
             case 64: TC_GO(64, 6, false);

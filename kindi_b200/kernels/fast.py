@@ -47,17 +47,26 @@ def _splits_for(m: int, n: int, k: int, bn: int) -> int:
     return best
 
 
-def _prefill_bn(m: int, n: int) -> int:
-    """the width of the weight side of a prefill tile: the one whose tiles fill whole rounds of the persistent CTAs
-    best (a round costs about its width; a partly filled last round costs a whole one)"""
+def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
+    """(columns of a tile, row tiles per unit) for a prompt-sized product: the pair with the least estimated time.
+    A K block of a unit costs what is slower, its MMAs (0.276 us for 128 x 256 x 64) or bringing its operand tiles
+    from the L2 (about 1.15 ns per operand row); two row tiles over one weight tile halve the weight traffic per
+    FLOP but leave the epilogue exposed; units fill the persistent CTAs in rounds and a partly filled round costs a
+    whole one."""
     if n <= 64:
-        return 64
-    best, best_cost = 128, None
-    for bn in (256, 224, 192, 160, 128):
-        units = -(-m // 128) * -(-n // bn)
-        cost = -(-units // N_SM) * (bn + 32)
-        if best_cost is None or cost < best_cost:
-            best, best_cost = bn, cost
+        return 64, 1
+    kb = -(-k // 64)
+    best, best_cost = (128, 1), None
+    for mt in ((1, 2) if m >= 256 else (1,)):
+        for bn in (256, 224, 192, 160, 128):
+            if swiglu and bn not in (128, 256):
+                continue
+            units = -(-m // (128 * mt)) * -(-n // bn)
+            t_kb = max(0.276 * mt * bn / 256.0, 1.15e-3 * (128 * mt + bn))
+            epilogue = (0.02 if mt == 2 else 0.004) * bn * mt
+            cost = -(-units // N_SM) * (kb * t_kb + epilogue)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = (bn, mt), cost
     return best
 
 
@@ -68,7 +77,8 @@ def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
     if m <= SMALL_M:
         K.gemm_tc(a, w, out, swap=True, bn=_swap_bn(m), splits=1, status=status)
     else:
-        K.gemm_tc(a, w, out, swap=False, bn=_prefill_bn(m, n), splits=1, status=status)
+        bn, mt = _prefill_tile(m, n, a.shape[1])
+        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=status, mt=mt)
     return True
 
 
@@ -85,7 +95,8 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
         K.gemm_tc(a, w, out, swap=True, bn=bn, splits=want, status=status)
         return out
     out = torch.empty((1, m, n), dtype=torch.float32, device=a.device)
-    K.gemm_tc(a, w, out[0], swap=False, bn=_prefill_bn(m, n), splits=1, status=status)
+    bn, mt = _prefill_tile(m, n, k)
+    K.gemm_tc(a, w, out[0], swap=False, bn=bn, splits=1, status=status, mt=mt)
     return out
 
 
@@ -95,8 +106,8 @@ def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor
     m, n = a.shape[0], w_grouped.shape[0]
     if m <= SMALL_M or not _tc_ok(a, w_grouped) or n % 128 or not out.is_contiguous() or (n // 2) % 8:
         return False
-    bn = _prefill_bn(m, n)
-    K.gemm_tc(a, w_grouped, out, swap=False, bn=bn if bn in (128, 256) else 256, splits=1, status=status, swiglu=True)
+    bn, mt = _prefill_tile(m, n, a.shape[1], swiglu=True)
+    K.gemm_tc(a, w_grouped, out, swap=False, bn=bn, splits=1, status=status, swiglu=True, mt=mt)
     return True
 
 

@@ -40,7 +40,7 @@ _SIGS = {
                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                   c_longlong, c_void_p, c_void_p, c_int],
+                   c_longlong, c_void_p, c_void_p, c_int, c_int],
     "kb_gemm_tc_splits": [c_int, c_int],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -218,11 +218,11 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,
-            status: torch.Tensor, swiglu: bool = False) -> None:
+            status: torch.Tensor, swiglu: bool = False, mt: int = 1) -> None:
     """out = a[M, K] @ w[N, K]^T on the tensor cores (bf16 in, fp32 accumulate). ``out`` is [M, N] (bf16 or fp32)
     or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits). ``swiglu`` (prefill form, bn 128 or 256):
     w holds 64 gate rows then the 64 up rows of the same outputs, group after group, and ``out`` is the bf16
-    [M, N / 2] result silu(gate) * up"""
+    [M, N / 2] result silu(gate) * up. ``mt`` = 2 (prefill form): a unit is two 128-row tiles over the same columns"""
     _need_cuda(a, w, out)
     M, K = a.shape
     N = w.shape[0]
@@ -238,7 +238,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, 
         assert out.shape == (M, N) and splits == 1
         stride, ldc = 0, N
     _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, 1 if swap else 0,
-                             bn, splits, stride, _p(status), _stream(), 1 if swiglu else 0), "gemm_tc")
+                             bn, splits, stride, _p(status), _stream(), 1 if swiglu else 0, mt), "gemm_tc")
 
 
 def gemm_tc_splits(K: int, wanted: int) -> int:

@@ -227,3 +227,26 @@ def test_attention_tc_prefill(K, nh, nkv, window):
     err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, 128, [300], [300], window=window, seed=nh + 2,
                          boost=(0, 299, 250))
     assert err < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 128), (2048, 2560, 1096, 160), (300, 700, 200, 192),
+                                       (513, 1000, 136, 224), (1000, 520, 264, 256)])
+def test_gemm_tc_two_row_tiles(K, M, N, K_, bn):
+    g = torch.Generator(device="cuda").manual_seed(M + N + K_)
+    a = torch.randn(M, K_, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K_, device="cuda", generator=g).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    st = _status()
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 5e-3)):
+        out = torch.full((M, N), float("nan"), device="cuda", dtype=dtype)
+        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=st, mt=2)
+        assert int(st.item()) == 0
+        assert _rel(out.float(), ref) < tol
+    if bn in (128, 256) and N % 128 == 0:
+        F = N // 2
+        wg, wu = w[:F], w[F:]
+        wgu = torch.stack([wg.view(F // 64, 64, K_), wu.view(F // 64, 64, K_)], dim=1).reshape(N, K_).contiguous()
+        h = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+        K.gemm_tc(a * 0.1, wgu, h, swap=False, bn=bn, splits=1, status=st, swiglu=True, mt=2)
+        gg, uu = (a * 0.1).double() @ wg.double().T, (a * 0.1).double() @ wu.double().T
+        assert _rel(h.float(), gg / (1 + torch.exp(-gg)) * uu) < 6e-3
