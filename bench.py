@@ -168,7 +168,7 @@ def bench_decode(eng, batch: int, context: int, steps: int, warmup: int, e2e: bo
 
     def one(toks):
         entries = [StepEntry(s, (t,), (0,)) for s, t in zip(slots, toks)]
-        return stepper.sampler.pick(eng.step(entries), greedy)
+        return eng.step(entries, greedy=True)[1]
 
     for _ in range(max(3, warmup)):
         one(toks)

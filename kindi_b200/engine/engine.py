@@ -28,6 +28,7 @@ from ..weights.loader import load_tensors
 from .batch import PackedStep, StepEntry, pack
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+from ..config.runtime import GREEDY as _GREEDY      # noqa: E402
 
 
 class EngineError(RuntimeError):
@@ -89,9 +90,12 @@ class Engine:
         return self.cache.length[slot]
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], greedy: bool = False):
         """run the entries' tokens as one batch; returns float32 logits ``[number of wanted places, vocab]`` on the
-        device (None when nothing is wanted). The cache then holds the tokens' keys and values."""
+        device (None when nothing is wanted). The cache then holds the tokens' keys and values. With ``greedy`` the
+        return value is ``(logits, tokens)``, ``tokens`` being the argmax of each wanted row (int32, on the device;
+        in the recorded decode step the pick is part of the recording). The tensors belong to the engine until its
+        next step."""
         cache = self.cache
         before = [cache.length[e.slot] for e in entries]
         ps = pack(entries, before)
@@ -114,8 +118,10 @@ class Engine:
             if graph is None and ps.B in self._graph_warm:
                 graph = self._graphs[ps.B] = _DecodeGraph(self, ps)
             self._graph_warm.add(ps.B)
+        picked = None
         if graph is not None:
             logits = graph.replay(ps)
+            picked = graph.picked
             self.graph_replays += 1
         else:
             ctx = self._context(ps)
@@ -127,7 +133,17 @@ class Engine:
         for e, new_len in zip(entries, ps.h_kv_len):
             cache.commit(e.slot, new_len)
         self.steps_run += 1
+        if greedy:
+            if picked is None and logits is not None:
+                picked = self._sampler().pick(logits, _GREEDY)
+            return logits, picked
         return logits
+
+    def _sampler(self):
+        if getattr(self, "_sampler_obj", None) is None:
+            from ..sampling.sampler import Sampler
+            self._sampler_obj = Sampler(self.device)
+        return self._sampler_obj
 
     def _context(self, ps: PackedStep, dev: Optional[torch.Tensor] = None) -> StepContext:
         if dev is not None:
@@ -242,6 +258,7 @@ class _DecodeGraph:
         try:
             with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
                 self.logits = engine.model.forward(ctx, rows)
+                self.picked = engine._sampler().pick(self.logits, _GREEDY)      # the greedy pick rides along
         finally:
             if was_on:
                 gc.enable()
@@ -280,6 +297,11 @@ class EngineStepper:
 
     def run(self, entries, params, seq_ids, histories) -> List[int]:
         from ..sampling.sampler import SequenceRandom
+        if params.greedy and (params.repeat_penalty == 1.0 or histories is None):
+            _, picked = self.engine.step(entries, greedy=True)
+            toks = picked.tolist()
+            self.engine.check_status()
+            return toks
         logits = self.engine.step(entries)
         uniforms = None
         if not params.greedy:
