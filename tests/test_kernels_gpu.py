@@ -250,3 +250,97 @@ def test_gemm_tc_two_row_tiles(K, M, N, K_, bn):
         K.gemm_tc(a * 0.1, wgu, h, swap=False, bn=bn, splits=1, status=st, swiglu=True, mt=2)
         gg, uu = (a * 0.1).double() @ wg.double().T, (a * 0.1).double() @ wu.double().T
         assert _rel(h.float(), gg / (1 + torch.exp(-gg)) * uu) < 6e-3
+
+
+# ------------------------------------------------------------------------------------------------ small kernels
+@pytest.mark.parametrize("T,E,planes", [(3, 50, 0), (8, 2560, 7), (5, 72, 3), (600, 2560, 1), (600, 96, 9), (70, 4100, 2)])
+@pytest.mark.parametrize("ydtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(K, T, E, planes, ydtype):
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x0 = torch.randn(T, E, device="cuda", generator=g)
+    d = torch.randn(planes, T, E, device="cuda", generator=g) * 0.3 if planes else None
+    for wdtype in (torch.float32, torch.bfloat16):
+        w = (1 + 0.1 * torch.randn(E, device="cuda", generator=g)).to(wdtype)
+        x = x0.clone()
+        y = torch.empty(T, E, device="cuda", dtype=ydtype)
+        st = _status()
+        K.add_rmsnorm(x, d, w, 1e-5, y, None, write_back=d is not None, status=st)
+        v = x0.double() + (d.double().sum(0) if planes else 0)
+        ref = v / torch.sqrt((v * v).mean(-1, keepdim=True) + 1e-5) * w.double()
+        assert _rel(x, v) < 1e-6 and _rel(y.float(), ref) < (2e-6 if ydtype == torch.float32 else 6e-3)
+        # a gather of rows, nothing written back
+        rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32).cuda()
+        x2 = x0.clone()
+        y2 = torch.empty(3, E, device="cuda", dtype=ydtype)
+        K.add_rmsnorm(x2, d, w, 1e-5, y2, rows, write_back=False, status=st)
+        assert torch.equal(x2, x0) and _rel(y2.float(), ref[rows.long()]) < (2e-6 if ydtype == torch.float32 else 6e-3)
+        K.add_rmsnorm(x2, None, w, 1e-5, y2, torch.tensor([T, -1, 0], dtype=torch.int32).cuda(), write_back=False, status=st)
+        assert int(st.item()) == K.ST_BAD_ROW                     # reported, not a fault
+
+
+@pytest.mark.parametrize("T,F,group,planes", [(3, 50, 0, 0), (9, 193, 0, 3), (8, 10496, 64, 5), (700, 320, 64, 0),
+                                              (130, 64, 64, 1)])
+def test_swiglu(K, T, F, group, planes):
+    g = torch.Generator(device="cuda").manual_seed(T + F)
+    gate = torch.randn(T, F, device="cuda", generator=g) * 2
+    up = torch.randn(T, F, device="cuda", generator=g)
+    ref = gate.double() / (1 + torch.exp(-gate.double())) * up.double()
+    gp = group or F
+    gu = torch.stack([gate.view(T, F // gp, gp), up.view(T, F // gp, gp)], dim=2).reshape(T, 2 * F).contiguous()
+    for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 1.5e-2)):
+        out = torch.empty(T, F, device="cuda", dtype=dtype)
+        K.swiglu(gu.to(dtype), out, group)
+        assert _rel(out.float(), ref) < tol
+    if planes:
+        parts = torch.randn(planes, T, 2 * F, device="cuda", generator=g)
+        parts[-1] = gu - parts[:-1].sum(0)
+        out = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
+        K.swiglu(parts.contiguous(), out, group)
+        assert _rel(out.float(), ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("T,nh,nkv,hd,rot,planes", [(5, 3, 1, 48, 32, 0), (40, 20, 4, 128, 128, 0), (8, 20, 4, 128, 128, 5),
+                                                    (33, 2, 2, 18, 6, 0)])
+def test_rope_store_against_plain(K, T, nh, nkv, hd, rot, planes):
+    """rotation of q in place or from planes, keys rotated into the cache pages, values copied; both kernels
+    (one block per head for small steps, one block per row for larger ones) against the same formulas"""
+    g = torch.Generator().manual_seed(T + hd)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, generator=g)
+    pos = torch.arange(100, 100 + T, dtype=torch.int32)
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    inv = (10000.0 ** (-2 * i / rot)).float()
+    ang = (pos.float()[:, None] * inv[None]).double()
+    cos, sin = torch.cos(ang), torch.sin(ang)
+
+    def rot_ref(x):                      # [T, heads, hd]
+        a, b, rest = x[..., : rot // 2], x[..., rot // 2: rot], x[..., rot:]
+        return torch.cat([a * cos[:, None] - b * sin[:, None], b * cos[:, None] + a * sin[:, None], rest], -1)
+    q_ref = rot_ref(qkv[:, : nh * hd].double().view(T, nh, hd))
+    k_ref = rot_ref(qkv[:, nh * hd: (nh + nkv) * hd].double().view(T, nkv, hd))
+    v_ref = qkv[:, (nh + nkv) * hd:].double().view(T, nkv, hd)
+    n_pages = 4
+    table = torch.tensor([[2, 0, 3, 1]], dtype=torch.int32).cuda()          # positions 100.. lie in blocks 1 and 2
+    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 6e-3)):
+        pool = torch.zeros(n_pages, 2, nkv, 64, hd, dtype=dtype, device="cuda")
+        st = _status()
+        seq = torch.zeros(T, dtype=torch.int32).cuda()
+        slot = torch.zeros(1, dtype=torch.int32).cuda()
+        if planes:
+            if dtype == torch.float32:
+                continue
+            parts = torch.randn(planes, T, width, generator=g)
+            parts[-1] = qkv - parts[:-1].sum(0)
+            src = parts.cuda().contiguous()
+            qout = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+        else:
+            src = qkv.to(dtype).cuda()
+            qout = src
+        K.rope_store(src, qout, inv.cuda(), rot, pos.cuda(), seq, slot, nh, nkv, hd, pool, table, n_pages, st)
+        assert int(st.item()) == 0
+        assert _rel(qout[:, : nh * hd].float().cpu().view(T, nh, hd), q_ref) < tol
+        for t in range(T):
+            p = 100 + t
+            page = int(table[0, p // 64])
+            assert _rel(pool[page, 0, :, p % 64].float().cpu(), k_ref[t]) < tol
+            assert _rel(pool[page, 1, :, p % 64].float().cpu(), v_ref[t]) < tol
