@@ -418,7 +418,7 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
 // ------------------------------------------------------------------------------------------------------------------
 // Decode attention for callers that cannot allocate device memory (declared in kindi_b200_noalloc.h; the reference has
 // no counterpart). Some hosts of this library may not call cudaMalloc at all: a plug-in that runs inside another
-// program's CUDA context under a fixed memory budget, a real-time loop that must not touch the allocator once it is
+// program's CUDA context under a fixed memory limit, a real-time loop that must not touch the allocator once it is
 // running, a process whose memory pool is owned by somebody else. kb_attn_mma above needs scratch for the partial
 // results of its position splits and takes it from its caller (who gets it from an allocator); this entry point runs
 // the same kernels with that scratch in the file-scope array below instead, so it allocates nothing: no cudaMalloc,

@@ -1,7 +1,7 @@
 /* kindi_b200: the one entry point of the kernel library that allocates nothing.
  *
  * It has no counterpart in ahtx/kindi; it exists for hosts that cannot allocate device memory while they run (a
- * plug-in inside another program's CUDA context with a fixed memory budget, a real-time loop that keeps away from
+ * plug-in inside another program's CUDA context with a fixed memory limit, a real-time loop that keeps away from
  * the allocator, a process whose memory pool belongs to somebody else).
  *
  * kb_attn_decode_static runs this library's decode attention over the paged cache (bfloat16, head size 64 or 128,

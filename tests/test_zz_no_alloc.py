@@ -1,7 +1,7 @@
 """The entry point that allocates nothing, kb_attn_decode_static, called through its exported C symbol.
 
 Who needs it: a host that may not allocate device memory while it runs (a plug-in inside another program's CUDA
-context with a fixed budget, a real-time loop, a process whose memory pool belongs to somebody else). The usual
+context with a fixed memory limit, a real-time loop, a process whose memory pool belongs to somebody else). The usual
 decode attention (kb_attn_mma) takes the scratch for its position splits from its caller; this one keeps it in a
 static device array of the library (4 MiB per GPU). The test checks, on two calls in a row with different inputs,
 that it gives what the usual entry point gives with scratch from the allocator, that device memory in use does not
