@@ -64,3 +64,23 @@ def test_replay_modes_match_plain(models, tmp_path, name, dtype):
         for key, row in results["whole"].items():
             assert np.array_equal(row, results["last32"][key]), ("last32", key)
             assert np.array_equal(row, results["batched"][key]), ("batched", key)
+
+
+@pytest.mark.parametrize("stored,run", [("float32", "bfloat16"), ("bfloat16", "float32")])
+def test_folder_stored_in_the_other_dtype(models, tmp_path, stored, run):
+    """a 32-bit folder run in bfloat16 keeps its tensors in 32-bit (the products then take 32-bit weights and bfloat16
+    activations); a bfloat16 folder run in 32-bit is widened exactly"""
+    from kindi_b200.engine.engine import Engine
+    model_dir = models[("C", stored)]
+    reqs = tiny.random_requests(331, [40, 3, 70], seed=5)
+    m = P.load_model(model_dir)
+    steps = tiny.trace_batched(reqs, batch=3, decode=8)
+    eng = Engine(model_dir, ctx=tiny.max_live_tokens(steps), dtype=run, max_batch=3)
+    want_dtype = torch.float32 if stored == "float32" or run == "float32" else torch.bfloat16
+    assert eng.model.embedding.dtype == want_dtype and eng.model.blocks[0].mixer.wqkv.dtype == want_dtype
+    out = str(tmp_path / "o")
+    tiny.run_replay(eng, steps, out)
+    got = tiny.collect(out, steps, 331)
+    for rid, toks in reqs.items():
+        mine = np.stack([got[(rid, i)] for i in range(len(toks))])
+        assert tiny.rel_err(mine, P.forward(m, toks).numpy()) <= TOL[run]
