@@ -344,3 +344,19 @@ def test_rope_store_against_plain(K, T, nh, nkv, hd, rot, planes):
             page = int(table[0, p // 64])
             assert _rel(pool[page, 0, :, p % 64].float().cpu(), k_ref[t]) < tol
             assert _rel(pool[page, 1, :, p % 64].float().cpu(), v_ref[t]) < tol
+
+
+@pytest.mark.parametrize("kind,hd,dtype", [("generic", 48, torch.float32), ("generic", 128, torch.bfloat16),
+                                           ("prefill", 64, torch.bfloat16), ("decode", 128, torch.bfloat16),
+                                           ("decode", 64, torch.bfloat16), ("tc", 128, torch.bfloat16)])
+def test_attention_window_edge(K, kind, hd, dtype):
+    """a key that stands out, placed on the last position a row may still see (pos - window + 1) and on the first it
+    may not (pos - window): an off-by-one at the window's edge then changes the output grossly, not by a few per cent"""
+    window, kv = 100, 300
+    ql = 1 if kind == "decode" else 40
+    row = ql - 1
+    pos_row = kv - 1
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    for key in (pos_row - window + 1, pos_row - window):
+        err = _run_attention(K, kind, dtype, 4, 2, hd, [ql, 1], [kv, 70], window, seed=hd + key, boost=(0, row, key))
+        assert err < tol, (kind, key, err)
