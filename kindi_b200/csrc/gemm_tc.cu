@@ -327,7 +327,7 @@ extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int
         switch (bn) {
             case 16: TC_GO(16, 8, true);
             case 32: TC_GO(32, 8, true);
-            case 64: TC_GO(64, 6, true);
+            case 64: TC_GO(64, 8, true);
             case 128: TC_GO(128, 5, true);
             default: return (int)cudaErrorInvalidValue;
         }
