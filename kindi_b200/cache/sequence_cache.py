@@ -100,13 +100,12 @@ class SequenceCache:
         self.length[slot] = 0
 
     def reserve(self, slot: int, new_len: int) -> None:
-        """map pages so that positions below new_len can be written and read; raises CacheFull (nothing changed)"""
+        """map pages so that positions below new_len can be written and read. Raises CacheFull when a group has no
+        page left; pages mapped before that stay with the slot (they are given back with it)"""
         if not self.slots.held(slot):
             raise CacheError("slot %d is not in use" % slot)
-        done: List[KVGroup] = []
         for g in self.groups:
             g.pages.ensure(slot, new_len)
-            done.append(g)
 
     def commit(self, slot: int, new_len: int) -> None:
         """the step that stored positions up to new_len has been issued"""

@@ -144,16 +144,29 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* __restrict__ x,
     float* xr = x + (size_t)t * E;
     const float* dr = delta + (size_t)t * E;
     float ss = 0.0f;
-    for (int i = lane * 4; i < E; i += 128) {
-        float4 v = *(const float4*)(xr + i);
+    // four chunks of the row at a time: all their loads are issued before the first sum is stored (a store to the
+    // row would otherwise hold back the loads behind it)
+    for (int i0 = lane * 4; i0 < E; i0 += 4 * 128) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (i0 + u * 128 < E) v[u] = *(const float4*)(xr + i0 + u * 128);
         if (n_delta > 0) {
-            v = kb_sum_planes4(v, dr + i, n_delta, delta_stride);
-            *(float4*)(xr + i) = v;
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (i0 + u * 128 < E) v[u] = kb_sum_planes4(v[u], dr + i0 + u * 128, n_delta, delta_stride);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (i0 + u * 128 < E) *(float4*)(xr + i0 + u * 128) = v[u];
         }
-        ss = fmaf(v.x, v.x, ss);
-        ss = fmaf(v.y, v.y, ss);
-        ss = fmaf(v.z, v.z, ss);
-        ss = fmaf(v.w, v.w, ss);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (i0 + u * 128 < E) {
+                ss = fmaf(v[u].x, v[u].x, ss);
+                ss = fmaf(v[u].y, v[u].y, ss);
+                ss = fmaf(v[u].z, v[u].z, ss);
+                ss = fmaf(v[u].w, v[u].w, ss);
+            }
     }
     ss = kb_warp_sum(ss);
     const float scale = rsqrtf(ss / (float)E + eps);

@@ -60,7 +60,6 @@ class Engine:
             spec = architecture(self.config.architecture).build_spec(self.config)
         self.spec = spec
         if tensors is None:
-            optional = ()
             tensors = load_tensors(model_dir, expected_tensors(spec), run_dtype=dtype, device=str(self.device))
         else:
             tensors = {n: _to_run_dtype(t, dtype).to(self.device) for n, t in tensors.items()}
@@ -99,7 +98,6 @@ class Engine:
         cache = self.cache
         before = [cache.length[e.slot] for e in entries]
         ps = pack(entries, before)
-        limit = self.spec.max_positions
         reserved = []
         try:
             for e, new_len in zip(entries, ps.h_kv_len):
