@@ -9,7 +9,12 @@ import torch
 
 from . import lib as K
 
-N_SM = 148                 # B200: 2 dies x 74 SMs
+N_SM = 148                 # B200: 2 dies x 74 SMs (replaced by the device's own count when a GPU is present)
+try:
+    if torch.cuda.is_available():
+        N_SM = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+except Exception:                                       # noqa: BLE001
+    pass
 SMALL_M = 128              # up to here the weights go through the 128-row side of the MMA ("swap" form)
 
 
