@@ -92,3 +92,26 @@ def pack(entries: Sequence[StepEntry], length_before: Sequence[int]) -> PackedSt
     seg("rows")[:] = rows
     return PackedStep(T=T, B=B, R=R, meta=meta, off=off, h_slot=tuple(slots), h_q_start=tuple(q_start),
                       h_kv_len=tuple(kv_len), decode=max(q_len) == 1, max_q=max(q_len), max_kv=max(kv_len))
+
+
+def split_step(entries: Sequence[StepEntry], chunk: int) -> List[List[Tuple[int, StepEntry]]]:
+    """cut a step that brings more than ``chunk`` tokens into sub-steps of at most ``chunk`` tokens each: sequences
+    are taken in order and a long one continues in the next sub-step (its later tokens read the earlier ones from
+    the cache, as the reference's prompt chunks do, ``kindi/nanbeige.py:943-946,974``). Returns, per sub-step, a list
+    of (index of the original entry, its share); ``want`` places are moved to the share that holds them. A slot
+    appears at most once in a sub-step."""
+    subs: List[List[Tuple[int, StepEntry]]] = [[]]
+    room = chunk
+    for i, e in enumerate(entries):
+        at = 0
+        n = len(e.tokens)
+        while at < n:
+            if room == 0 or any(j == i for j, _ in subs[-1]):
+                subs.append([])
+                room = chunk
+            take = min(room, n - at)
+            want = tuple(w - at for w in e.want if at <= w < at + take)
+            subs[-1].append((i, StepEntry(e.slot, e.tokens[at:at + take], want)))
+            at += take
+            room -= take
+    return subs

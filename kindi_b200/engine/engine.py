@@ -25,7 +25,7 @@ from ..kernels import lib as K
 from ..parts.base import StepContext
 from ..parts.model import DecoderModel, cache_needs, expected_tensors
 from ..weights.loader import load_tensors
-from .batch import PackedStep, StepEntry, pack
+from .batch import PackedStep, StepEntry, pack, split_step
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 from ..config.runtime import GREEDY as _GREEDY      # noqa: E402
@@ -38,7 +38,8 @@ class EngineError(RuntimeError):
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, ctx: int = 24576, dtype: str = "bfloat16",
                  max_batch: int = 64, device: str = "cuda:0", spec: Optional[ModelSpec] = None,
-                 tensors: Optional[Mapping[str, torch.Tensor]] = None, cuda_graphs: bool = True, log=None):
+                 tensors: Optional[Mapping[str, torch.Tensor]] = None, cuda_graphs: bool = True,
+                 max_step_tokens: int = 8192, log=None):
         """``model_dir``: a folder with config.json and safetensors files; or give ``spec`` and ``tensors``
         directly. ``ctx``: the most tokens all live sequences hold together (rounded up per sequence to the cache
         page); it sizes the cache, like the reference's ``ctx`` (``kindi/nanbeige.py:245``)."""
@@ -71,6 +72,7 @@ class Engine:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
+        self.max_step_tokens = max(64, int(max_step_tokens))     # longer steps are run in pieces of this many tokens
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self.graph_replays = 0
@@ -95,6 +97,8 @@ class Engine:
         return value is ``(logits, tokens)``, ``tokens`` being the argmax of each wanted row (int32, on the device;
         in the recorded decode step the pick is part of the recording). The tensors belong to the engine until its
         next step."""
+        if sum(len(e.tokens) for e in entries) > self.max_step_tokens:
+            return self._step_in_pieces(entries, greedy)
         cache = self.cache
         before = [cache.length[e.slot] for e in entries]
         ps = pack(entries, before)
@@ -135,6 +139,27 @@ class Engine:
             if picked is None and logits is not None:
                 picked = self._sampler().pick(logits, _GREEDY)
             return logits, picked
+        return logits
+
+    def _step_in_pieces(self, entries: Sequence[StepEntry], greedy: bool):
+        """a step of more than max_step_tokens tokens: its pieces run one after another (activations stay bounded;
+        a later piece reads the earlier ones from the cache) and the wanted rows are put back in the order of the
+        entries and of their ``want`` lists"""
+        pieces = split_step(entries, self.max_step_tokens)
+        got: Dict[Tuple[int, int], torch.Tensor] = {}            # (entry, place) -> logits row
+        offset = [0] * len(entries)
+        for sub in pieces:
+            logits = self.step([e for _, e in sub])
+            row = 0
+            for i, e in sub:
+                for w in e.want:
+                    got[(i, offset[i] + w)] = logits[row].clone()
+                    row += 1
+                offset[i] += len(e.tokens)
+        order = [(i, w) for i, e in enumerate(entries) for w in e.want]
+        logits = torch.stack([got[k] for k in order]) if order else None
+        if greedy:
+            return logits, (self._sampler().pick(logits, _GREEDY) if logits is not None else None)
         return logits
 
     def _sampler(self):

@@ -2,7 +2,7 @@
 import pytest
 
 from kindi_b200.config.runtime import SamplingParams
-from kindi_b200.engine.batch import StepEntry, layout, pack
+from kindi_b200.engine.batch import StepEntry, layout, pack, split_step
 from kindi_b200.engine.generate import PromptTooLong, generate, max_new_tokens, plan_batches
 
 
@@ -128,3 +128,21 @@ def test_pack_arithmetic():
     for bad in ([StepEntry(0, (), ())], [StepEntry(0, (1,), (1,))], [StepEntry(0, (1,)), StepEntry(0, (2,))], []):
         with pytest.raises(ValueError):
             pack(bad, [0] * len(bad))
+
+
+def test_split_step_keeps_every_token_and_place():
+    entries = [StepEntry(0, tuple(range(10)), (0, 9)), StepEntry(1, (7,), (0,)), StepEntry(2, tuple(range(100, 125)), (3, 24)),
+               StepEntry(3, (1, 2), ())]
+    for chunk in (4, 8, 11, 25, 64):
+        subs = split_step(entries, chunk)
+        assert all(sum(len(e.tokens) for _, e in sub) <= chunk for sub in subs)
+        assert all(len({e.slot for _, e in sub}) == len(sub) for sub in subs)           # a slot once per sub-step
+        seen = {i: [] for i in range(len(entries))}
+        places = {i: [] for i in range(len(entries))}
+        for sub in subs:
+            for i, e in sub:
+                places[i] += [len(seen[i]) + w for w in e.want]
+                seen[i] += list(e.tokens)
+        for i, e in enumerate(entries):
+            assert tuple(seen[i]) == e.tokens and tuple(places[i]) == e.want
+    assert len(split_step(entries, 64)) == 1

@@ -84,3 +84,29 @@ def test_folder_stored_in_the_other_dtype(models, tmp_path, stored, run):
     for rid, toks in reqs.items():
         mine = np.stack([got[(rid, i)] for i in range(len(toks))])
         assert tiny.rel_err(mine, P.forward(m, toks).numpy()) <= TOL[run]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_steps_run_in_pieces(models, tmp_path, dtype):
+    """a step longer than max_step_tokens is run in pieces inside the step function; in 32-bit the logits are the
+    same bits as from one whole step"""
+    from kindi_b200.engine.engine import Engine
+    model_dir = models[("D", dtype)]
+    reqs = tiny.random_requests(500, [150, 9, 70, 33], seed=6)
+    steps = tiny.trace_batched(reqs, batch=4, decode=5)
+    m = P.load_model(model_dir)
+    outs = {}
+    for name, cap in (("whole", 8192), ("pieces", 64)):
+        eng = Engine(model_dir, ctx=tiny.max_live_tokens(steps), dtype=dtype, max_batch=4, max_step_tokens=cap)
+        out = str(tmp_path / name)
+        tiny.run_replay(eng, steps, out)
+        outs[name] = tiny.collect(out, steps, 500)
+        if name == "pieces":
+            assert eng.steps_run > len(steps)
+        eng.cache.check()
+    for rid, toks in reqs.items():
+        mine = np.stack([outs["pieces"][(rid, i)] for i in range(len(toks))])
+        assert tiny.rel_err(mine, P.forward(m, toks).numpy()) <= TOL[dtype]
+    if dtype == "float32":
+        for k, row in outs["whole"].items():
+            assert np.array_equal(row, outs["pieces"][k]), k
