@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
     bf16* qs = (bf16*)(smem + AT_STAGES * STAGE_BYTES + 2 * AT_STAGES * 8 + 16);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, hk = blockIdx.y;
-    kb_pdl_launch();
+    if (DEC) kb_pdl_launch_now();
     kb_pdl_wait();                               // the step's metadata, Q and the newest keys come from earlier kernels
     const int qs0 = q_start[b], qlen = q_start[b + 1] - qs0, kvl = kv_len[b];
     const int pos0 = kvl - qlen;                 // position of the sequence's first row of this step

@@ -63,7 +63,6 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
         const int* __restrict__ table, int table_stride, int n_pages, int* status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    kb_pdl_launch();
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t s_q = sbase, s_kv = s_q + FT_Q_BYTES, s_p = s_kv + FT_STAGES * FT_STAGE_BYTES;

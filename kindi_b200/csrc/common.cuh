@@ -57,13 +57,19 @@ __device__ __forceinline__ size_t kb_kv_offset(const KbCacheView& c, int page, i
 
 #define KB_LAUNCH_RET() return (int)cudaGetLastError()
 
-// Programmatic dependent launch. Every kernel of the library begins with kb_pdl_launch() (the next kernel of the
-// stream may be scheduled as soon as all CTAs of this one have started) and calls kb_pdl_wait() before its first
+// Programmatic dependent launch. Every kernel of the library begins with kb_pdl_launch() (when its grid is small,
+// the next kernel of the stream may be scheduled as soon as all CTAs of this one have started) and calls
+// kb_pdl_wait() before its first
 // read of anything an earlier kernel wrote and before its first global write (until then it may only set up
 // barriers and tensor memory and fetch weights, which no kernel writes). The wait returns when the whole preceding
 // kernel has finished and its writes are visible, so results are those of strictly ordered launches; what is
 // gained is that launch latency and prologues overlap the predecessor's tail.
-__device__ __forceinline__ void kb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void kb_pdl_launch_now() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Small grids (decode steps) let their successor start at once; large grids (prompt steps) do not: the successor's
+// blocks would only sit on the SMs beside blocks that still have work, and that was measured to cost more than it hides.
+__device__ __forceinline__ void kb_pdl_launch() {
+    if (gridDim.x * gridDim.y * gridDim.z <= 1024u) kb_pdl_launch_now();
+}
 __device__ __forceinline__ void kb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 extern int g_kb_pdl;            // 1: launches carry the programmatic-serialization attribute

@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
     using S = TcSmem<BN, STAGES, MT>;
     static_assert(MT == 1 || (!SWAP && 2 * BN <= 512), "two row tiles: prefill form, both accumulators in tensor memory");
     extern __shared__ uint8_t smem_raw[];
-    kb_pdl_launch();
+    if (SWAP) kb_pdl_launch_now();               // decode steps only (see common.cuh)
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar_full = sbase + S::BAR_OFF, bar_empty = bar_full + STAGES * 8;
@@ -80,25 +80,15 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         if (lane == 0) {
             uint32_t n = 0;                                  // k-blocks loaded so far (ring position)
             bool ok = true;
-            // In the decode form the 128-row side is the weights, which no kernel writes: their tiles are requested
-            // BEFORE the wait on the preceding kernel, so the ring is already filling while that kernel finishes;
-            // the activation tiles of those stages follow right after the wait.
-            bool waited = !SWAP;
-            int pend_kb[STAGES], pend_tq[STAGES], n_pend = 0;
-            if (!SWAP) kb_pdl_wait();
+            // (Requesting the decode form's weight tiles before this wait was tried: the early loads of all CTAs take the
+            // memory system from the small kernel that is still running, and the step got slower.)
+            kb_pdl_wait();
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 const int tp = u % tilesP, rest = u / tilesP, tq = rest % tilesQ, sp = rest / tilesQ;
                 const int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
                 for (int kb = kb0; kb < kb1; kb++, n++) {
                     const int s = n % STAGES;
                     const uint32_t ph = (n / STAGES) & 1u;
-                    if (!waited && n_pend == STAGES) {
-                        kb_pdl_wait();
-                        waited = true;
-                        for (int j = 0; j < n_pend; j++)
-                            tma_load_2d(sbase + j * S::STAGE_BYTES + S::A_BYTES, &mapQ, pend_kb[j] * TC_BK,
-                                        pend_tq[j] * BN, bar_full + j * 8);
-                    }
                     if (!(ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, status))) break;
                     mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
                     const uint32_t dst = sbase + s * S::STAGE_BYTES;
@@ -106,20 +96,8 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                     for (int m = 0; m < MT; m++)
                         tma_load_2d(dst + m * (TC_BM * TC_BK * 2), &mapP, kb * TC_BK, (tp * MT + m) * TC_BM,
                                     bar_full + s * 8);
-                    if (waited) {
-                        tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
-                    } else {
-                        pend_kb[n_pend] = kb;                // stage n_pend == s here: the ring has not wrapped yet
-                        pend_tq[n_pend] = tq;
-                        n_pend++;
-                    }
+                    tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
                 }
-            }
-            if (!waited) {
-                kb_pdl_wait();
-                for (int j = 0; j < n_pend; j++)
-                    tma_load_2d(sbase + j * S::STAGE_BYTES + S::A_BYTES, &mapQ, pend_kb[j] * TC_BK, pend_tq[j] * BN,
-                                bar_full + j * 8);
             }
         }
     } else if (warp == 1) {
