@@ -272,7 +272,7 @@ def main(argv=None) -> int:
     }
     if not a.no_points:
         T = PREFILL_TOKENS
-        pms = bench_prefill(eng, 3, 5)
+        pms = bench_prefill(eng, 5, 20)
         fl = prefill_flops(mc, T)
         out["prefill"] = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
                           "frac": round(fl / (pms / 1000.0) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"],

@@ -65,8 +65,9 @@ __device__ __forceinline__ size_t kb_kv_offset(const KbCacheView& c, int page, i
 // kernel has finished and its writes are visible, so results are those of strictly ordered launches; what is
 // gained is that launch latency and prologues overlap the predecessor's tail.
 __device__ __forceinline__ void kb_pdl_launch_now() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-// Small grids (decode steps) let their successor start at once; large grids (prompt steps) do not: the successor's
-// blocks would only sit on the SMs beside blocks that still have work, and that was measured to cost more than it hides.
+// Small grids (decode steps) let their successor start at once; large grids (prompt steps) do not: a successor that
+// was launched before its predecessor ended was measured to cost a prompt step several microseconds per kernel,
+// whether the trigger came at the start of the blocks or after their last loads.
 __device__ __forceinline__ void kb_pdl_launch() {
     if (gridDim.x * gridDim.y * gridDim.z <= 1024u) kb_pdl_launch_now();
 }
@@ -76,9 +77,21 @@ extern int g_kb_pdl;            // 1: launches carry the programmatic-serializat
 
 #ifdef __cplusplus
 #include <utility>
+// Every kernel of the library asks for the largest shared-memory partition of the SM, the one its tensor-core
+// kernels need: an SM re-partitions L1 and shared memory only when it is idle, so a step whose kernels all want the
+// same partition never waits for that, and a kernel launched early can become resident beside its predecessor.
+static inline void kb_same_partition(const void* kern) {
+    static const void* seen[64];
+    static int n_seen = 0;
+    for (int i = 0; i < n_seen; i++)
+        if (seen[i] == kern) return;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    if (n_seen < 64) seen[n_seen++] = kern;
+}
 template <typename... KArgs, typename... Args>
 static inline cudaError_t kb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                     Args&&... args) {
+    kb_same_partition((const void*)kern);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

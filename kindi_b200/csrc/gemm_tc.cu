@@ -17,6 +17,9 @@
 
 #define TC_BM 128
 #define TC_BK 64
+#ifndef TC_EARLY
+#define TC_EARLY 1               // stages of weights requested before the programmatic wait (decode form)
+#endif
 #define TC_THREADS 192          // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 
 template <int BN, int STAGES, int MT = 1>
@@ -80,15 +83,27 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         if (lane == 0) {
             uint32_t n = 0;                                  // k-blocks loaded so far (ring position)
             bool ok = true;
-            // (Requesting the decode form's weight tiles before this wait was tried: the early loads of all CTAs take the
-            // memory system from the small kernel that is still running, and the step got slower.)
-            kb_pdl_wait();
+            // In the decode form the 128-row side is the weights, which no kernel writes: the tiles of the first
+            // TC_EARLY stages are requested BEFORE the wait on the preceding kernel, so the first MMAs can start as
+            // soon as the activations are there. (Filling the whole ring early was measured slower: the loads of all
+            // CTAs take the memory system from the small kernel that is still running.)
+            constexpr int EARLY = SWAP ? TC_EARLY : 0;
+            bool waited = EARLY == 0;
+            int pend_kb[EARLY + 1], pend_tq[EARLY + 1], n_pend = 0;
+            if (waited) kb_pdl_wait();
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 const int tp = u % tilesP, rest = u / tilesP, tq = rest % tilesQ, sp = rest / tilesQ;
                 const int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
                 for (int kb = kb0; kb < kb1; kb++, n++) {
                     const int s = n % STAGES;
                     const uint32_t ph = (n / STAGES) & 1u;
+                    if (!waited && n_pend == EARLY) {
+                        kb_pdl_wait();
+                        waited = true;
+                        for (int j = 0; j < n_pend; j++)
+                            tma_load_2d(sbase + j * S::STAGE_BYTES + S::A_BYTES, &mapQ, pend_kb[j] * TC_BK,
+                                        pend_tq[j] * BN, bar_full + j * 8);
+                    }
                     if (!(ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, status))) break;
                     mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
                     const uint32_t dst = sbase + s * S::STAGE_BYTES;
@@ -96,8 +111,20 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                     for (int m = 0; m < MT; m++)
                         tma_load_2d(dst + m * (TC_BM * TC_BK * 2), &mapP, kb * TC_BK, (tp * MT + m) * TC_BM,
                                     bar_full + s * 8);
-                    tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
+                    if (waited) {
+                        tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, tq * BN, bar_full + s * 8);
+                    } else {
+                        pend_kb[n_pend] = kb;                // stage n_pend == s here: the ring has not wrapped yet
+                        pend_tq[n_pend] = tq;
+                        n_pend++;
+                    }
                 }
+            }
+            if (!waited) {
+                kb_pdl_wait();
+                for (int j = 0; j < n_pend; j++)
+                    tma_load_2d(sbase + j * S::STAGE_BYTES + S::A_BYTES, &mapQ, pend_kb[j] * TC_BK, pend_tq[j] * BN,
+                                bar_full + j * 8);
             }
         }
     } else if (warp == 1) {

@@ -180,6 +180,73 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* __restrict__ x,
     }
 }
 
+// One warp per row with the whole row in registers (widths up to NCH * 128): every load of the row and of the planes is
+// in flight before the first sum, and the row is read once. Same sums in the same order as k_add_rmsnorm_warp.
+template <typename TW, int NCH>
+__global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* __restrict__ x, const float* __restrict__ delta,
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float* xr = x + (size_t)t * E;
+    const float* dr = delta + (size_t)t * E;
+    float4 v[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+        const int i = (c * 32 + lane) * 4;
+        v[c] = i < E ? *(const float4*)(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int s = 0; s < n_delta; s++) {
+        const float* ds = dr + (size_t)s * delta_stride;
+#pragma unroll
+        for (int c0 = 0; c0 < NCH; c0 += 8) {
+            float4 d[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int i = ((c0 + j) * 32 + lane) * 4;
+                d[j] = (c0 + j < NCH && i < E) ? *(const float4*)(ds + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (c0 + j < NCH) {
+                    v[c0 + j].x += d[j].x;
+                    v[c0 + j].y += d[j].y;
+                    v[c0 + j].z += d[j].z;
+                    v[c0 + j].w += d[j].w;
+                }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+        const int i = (c * 32 + lane) * 4;
+        if (i < E) {
+            if (n_delta > 0) *(float4*)(xr + i) = v[c];
+            ss = fmaf(v[c].x, v[c].x, ss);
+            ss = fmaf(v[c].y, v[c].y, ss);
+            ss = fmaf(v[c].z, v[c].z, ss);
+            ss = fmaf(v[c].w, v[c].w, ss);
+        }
+    }
+    ss = kb_warp_sum(ss);
+    const float scale = rsqrtf(ss / (float)E + eps);
+    bf16* yr = y + (size_t)t * E;
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+        const int i = (c * 32 + lane) * 4;
+        if (i < E) {
+            const float w0 = kb_to_f<TW>(w[i]), w1 = kb_to_f<TW>(w[i + 1]), w2 = kb_to_f<TW>(w[i + 2]),
+                        w3 = kb_to_f<TW>(w[i + 3]);
+            __nv_bfloat162 a = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(scale, v[c].x), w0),
+                                                     __fmul_rn(__fmul_rn(scale, v[c].y), w1));
+            __nv_bfloat162 b = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(scale, v[c].z), w2),
+                                                     __fmul_rn(__fmul_rn(scale, v[c].w), w3));
+            *(uint2*)(yr + i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+        }
+    }
+}
+
 extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long long delta_stride, const void* w,
                               int wdtype, float eps, void* y, int ydtype, const int* rows, int n_out, int T, int E,
                               int write_back, int* status, cudaStream_t st) {
@@ -191,6 +258,20 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
     cudaError_t e = cudaSuccess;
     if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= 512 && (write_back || n_delta == 0) &&
         (((uintptr_t)y) % 8) == 0) {
+#define KB_NORM_REGS(NCH)                                                                                          \
+    do {                                                                                                           \
+        if (wdtype == KB_F32)                                                                                      \
+            e = kb_launch(k_add_rmsnorm_regs<float, NCH>, (T + 7) / 8, 256, 0, st, x, delta, n_delta,              \
+                          (size_t)delta_stride, (const float*)w, eps, (bf16*)y, T, E);                             \
+        else                                                                                                       \
+            e = kb_launch(k_add_rmsnorm_regs<bf16, NCH>, (T + 7) / 8, 256, 0, st, x, delta, n_delta,               \
+                          (size_t)delta_stride, (const bf16*)w, eps, (bf16*)y, T, E);                              \
+        return (int)e;                                                                                             \
+    } while (0)
+        if (E <= 8 * 128) KB_NORM_REGS(8);
+        if (E <= 16 * 128) KB_NORM_REGS(16);
+        if (E <= 24 * 128) KB_NORM_REGS(24);
+#undef KB_NORM_REGS
         if (wdtype == KB_F32)
             e = kb_launch(k_add_rmsnorm_warp<float>, (T + 7) / 8, 256, 0, st, x, delta, n_delta, (size_t)delta_stride,
                           (const float*)w, eps, (bf16*)y, T, E);
@@ -453,6 +534,138 @@ __global__ void __launch_bounds__(256) k_rope_store_row(const TIN* __restrict__ 
     }
 }
 
+// One block per row as above, eight neighbouring elements (16 or 32 bytes) per access: taken when rot % 16 == 0,
+// hd % 8 == 0 and everything is aligned for it. Same expressions, same bits.
+__device__ __forceinline__ void kb_ld8(const float* p, float* o) {
+    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void kb_ld8(const bf16* p, float* o) {
+    const uint4 r = *(const uint4*)p;
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)&w[j]);
+        o[2 * j] = f.x;
+        o[2 * j + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void kb_st8(float* p, const float* v) {
+    *(float4*)p = make_float4(v[0], v[1], v[2], v[3]);
+    *(float4*)(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void kb_st8(bf16* p, const float* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *(uint32_t*)&h;
+    }
+    *(uint4*)p = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// PLANES: the row is the sum of several planes (a decode step of many sequences). Without planes (a prompt) a thread
+// keeps few registers, so that most rows of a prompt are resident at once. Each thread requests its first item's
+// elements before it does anything else: those loads, the row's angles and its page lookup then wait side by side.
+template <typename TIN, typename T, bool PLANES>
+__global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const TIN* __restrict__ in, int n_planes,
+        size_t plane_stride, int ld_in, T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
+        const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
+        int hd, KbCacheView cv, int* status) {
+    extern __shared__ float2 cs[];                  // [rot / 2]: (cos, sin) of the row's angles
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int t = blockIdx.x;
+    const int half = rot / 2;
+    const TIN* row = in + (size_t)t * ld_in;
+    auto rd8 = [&](int e, float* v) {                // elements e .. e + 7 of the row: the planes added in order
+        kb_ld8(row + e, v);
+        if (PLANES) {
+            for (int s0 = 1; s0 < n_planes; s0 += 4) {
+                float tt[4][8];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (s0 + j < n_planes) kb_ld8(row + (size_t)(s0 + j) * plane_stride + e, tt[j]);
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (s0 + j < n_planes) {
+#pragma unroll
+                        for (int c = 0; c < 8; c++) v[c] += tt[j][c];
+                    }
+            }
+        }
+    };
+    // items of a row: rotated runs of eight pairs (query heads, then key heads), the runs past the rotated part of
+    // those heads, the runs of the value heads
+    const int per_head = half / 8, n_rot = (nh + nkv) * per_head;
+    const int tail8 = (hd - rot) / 8, n_tail = (nh + nkv) * tail8;
+    const int hd8 = hd / 8, n_items = n_rot + n_tail + nkv * hd8;
+    auto load_item = [&](int it, float* a, float* b) {
+        if (it < n_rot) {
+            const int h = it / per_head, i = (it % per_head) * 8;
+            rd8(h * hd + i, a);
+            rd8(h * hd + i + half, b);
+        } else if (it < n_rot + n_tail) {
+            const int h = (it - n_rot) / tail8, i = rot + ((it - n_rot) % tail8) * 8;
+            rd8(h * hd + i, a);
+        } else {
+            const int h = (it - n_rot - n_tail) / hd8, i = ((it - n_rot - n_tail) % hd8) * 8;
+            rd8((nh + nkv + h) * hd + i, a);
+        }
+    };
+    float a[8], b[8];
+    if ((int)threadIdx.x < n_items) load_item(threadIdx.x, a, b);
+
+    const int p = pos[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = __fmul_rn((float)p, inv_freq[i]);
+        cs[i] = make_float2(cosf(ang), sinf(ang));
+    }
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (nkv > 0) {
+        const int s = slot[seq[t]];
+        const int page = cv.table[(size_t)s * cv.table_stride + p / KB_PAGE];
+        if (page < 0 || page >= cv.n_pages) {
+            if (threadIdx.x == 0) atomicOr(status, KB_ST_BAD_PAGE);
+        } else {
+            kdst = (T*)cv.pool + kb_kv_offset(cv, page, 0, 0, p % KB_PAGE);
+            vdst = (T*)cv.pool + kb_kv_offset(cv, page, 1, 0, p % KB_PAGE);
+        }
+    }
+    __syncthreads();
+    const size_t head_stride = (size_t)KB_PAGE * hd;       // from one key/value head to the next inside a page
+    for (int it = threadIdx.x; it < n_items; it += blockDim.x) {
+        if (it != (int)threadIdx.x) load_item(it, a, b);
+        if (it < n_rot) {
+            const int h = it / per_head, i = (it % per_head) * 8;
+            T* dst;
+            if (h < nh) dst = qout + (size_t)t * ldq + (size_t)h * hd;
+            else if (kdst) dst = kdst + (size_t)(h - nh) * head_stride;
+            else continue;
+            float lo[8], hi[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float2 k = cs[i + c];
+                lo[c] = __fsub_rn(__fmul_rn(a[c], k.x), __fmul_rn(b[c], k.y));
+                hi[c] = __fadd_rn(__fmul_rn(b[c], k.x), __fmul_rn(a[c], k.y));
+            }
+            kb_st8(dst + i, lo);
+            kb_st8(dst + i + half, hi);
+        } else if (it < n_rot + n_tail) {
+            const int h = (it - n_rot) / tail8, i = rot + ((it - n_rot) % tail8) * 8;
+            T* dst;
+            if (h < nh) dst = qout + (size_t)t * ldq + (size_t)h * hd;
+            else if (kdst) dst = kdst + (size_t)(h - nh) * head_stride;
+            else continue;
+            kb_st8(dst + i, a);
+        } else if (vdst) {
+            const int h = (it - n_rot - n_tail) / hd8, i = ((it - n_rot - n_tail) % hd8) * 8;
+            kb_st8(vdst + (size_t)h * head_stride + i, a);
+        }
+    }
+}
+
 // in: [n_planes][T][ld_in] (the planes are summed in order); in_dtype may be 32-bit planes with a bf16 cache / qout
 extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in,
                              void* qout, int dtype, int ldq, const float* inv_freq, int rot, const int* pos,
@@ -466,8 +679,19 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
     const bool by_row = T >= 32 && rot % 4 == 0 && hd % 2 == 0 && ld_in % 2 == 0 && ldq % 2 == 0 && plane_stride % 2 == 0 &&
                         ((uintptr_t)in % (2 * in_el)) == 0 && ((uintptr_t)qout % (2 * out_el)) == 0 &&
                         ((uintptr_t)pool % (2 * out_el)) == 0 && rot / 2 * 8 <= 32 * 1024;
+    const bool by_row8 = by_row && rot % 16 == 0 && hd % 8 == 0 && ld_in % 8 == 0 && ldq % 8 == 0 &&
+                         plane_stride % 8 == 0 && ((uintptr_t)in % (8 * in_el)) == 0 &&
+                         ((uintptr_t)qout % (8 * out_el)) == 0 && ((uintptr_t)pool % (8 * out_el)) == 0;
 #define KB_RS(TIN, T_)                                                                                        \
-    if (by_row)                                                                                               \
+    if (by_row8 && n_planes > 1)                                                                              \
+        kb_launch(k_rope_store_row8<TIN, T_, true>, T, 256, (size_t)(rot / 2) * sizeof(float2), st,           \
+                  (const TIN*)in, n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos,  \
+                  seq, slot, nh, nkv, hd, cv, status);                                                        \
+    else if (by_row8)                                                                                         \
+        kb_launch(k_rope_store_row8<TIN, T_, false>, T, 256, (size_t)(rot / 2) * sizeof(float2), st,          \
+                  (const TIN*)in, n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos,  \
+                  seq, slot, nh, nkv, hd, cv, status);                                                        \
+    else if (by_row)                                                                                               \
         kb_launch(k_rope_store_row<TIN, T_>, T, 256, (size_t)(rot / 2) * sizeof(float2), st, (const TIN*)in,   \
                   n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos, seq, slot, nh,   \
                   nkv, hd, cv, status);                                                                       \

@@ -253,7 +253,8 @@ def test_gemm_tc_two_row_tiles(K, M, N, K_, bn):
 
 
 # ------------------------------------------------------------------------------------------------ small kernels
-@pytest.mark.parametrize("T,E,planes", [(3, 50, 0), (8, 2560, 7), (5, 72, 3), (600, 2560, 1), (600, 96, 9), (70, 4100, 2)])
+@pytest.mark.parametrize("T,E,planes", [(3, 50, 0), (8, 2560, 7), (5, 72, 3), (600, 2560, 1), (600, 96, 9), (70, 4100, 2),
+                                        (520, 1000, 2), (513, 2048, 0), (600, 3200, 1)])
 @pytest.mark.parametrize("ydtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(K, T, E, planes, ydtype):
     g = torch.Generator(device="cuda").manual_seed(T + E)
@@ -300,7 +301,7 @@ def test_swiglu(K, T, F, group, planes):
 
 
 @pytest.mark.parametrize("T,nh,nkv,hd,rot,planes", [(5, 3, 1, 48, 32, 0), (40, 20, 4, 128, 128, 0), (8, 20, 4, 128, 128, 5),
-                                                    (33, 2, 2, 18, 6, 0)])
+                                                    (33, 2, 2, 18, 6, 0), (64, 5, 1, 64, 32, 3), (36, 3, 1, 24, 12, 0)])
 def test_rope_store_against_plain(K, T, nh, nkv, hd, rot, planes):
     """rotation of q in place or from planes, keys rotated into the cache pages, values copied; both kernels
     (one block per head for small steps, one block per row for larger ones) against the same formulas"""
