@@ -42,6 +42,9 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * 8192 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
+#ifndef AT_EARLY
+#define AT_EARLY 2                   // pages of older positions requested before the programmatic wait (decode form)
+#endif
 template <int HD, bool DEC>
 __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constant__ CUtensorMap kvmap,
         const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
@@ -64,8 +67,11 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
     bf16* qs = (bf16*)(smem + AT_STAGES * STAGE_BYTES + 2 * AT_STAGES * 8 + 16);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, hk = blockIdx.y;
+    // The step's metadata (lengths, slots, page table) was written before the step's first kernel, and the pages of
+    // older positions by earlier steps. In the decode form only Q and the page of the newest position come from the
+    // kernel just before this one, so each thread waits for that kernel where it first needs them.
     if (DEC) kb_pdl_launch_now();
-    kb_pdl_wait();                               // the step's metadata, Q and the newest keys come from earlier kernels
+    else kb_pdl_wait();
     const int qs0 = q_start[b], qlen = q_start[b + 1] - qs0, kvl = kv_len[b];
     const int pos0 = kvl - qlen;                 // position of the sequence's first row of this step
     const int n_rows = qlen * G;
@@ -109,12 +115,19 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         if (lane == 0 && n_iter > 0) {
             tma_prefetch_desc(&kvmap);
             const int* trow = table + (size_t)slot[b] * table_stride;
+            bool waited = !DEC;
             for (int i = 0; i < n_iter; i++) {
                 const int s = i % AT_STAGES;
                 const uint32_t ph = (uint32_t)(i / AT_STAGES) & 1u;
+                if (DEC && !waited && (i >= AT_EARLY || pg_lo + i == (kvl - 1) / KB_PAGE)) {
+                    kb_pdl_wait();
+                    waited = true;
+                }
                 if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, status)) break;
                 int page = trow[pg_lo + i];
                 if (page < 0 || page >= n_pages) {
+                    if (!waited) kb_pdl_wait();              // the status word is shared with earlier kernels
+                    waited = true;
                     atomicOr(status, KB_ST_BAD_PAGE);
                     page = 0;
                 }
@@ -133,6 +146,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         // this warp's 16 rows: r = wrow0 + 0..15; thread rows ra = lane / 4, rb = ra + 8
         const int wrow0 = row0 + (DEC ? 0 : warp * 16);
         bf16* qw = qs + (DEC ? 0 : warp) * 16 * QS;
+        if (DEC) kb_pdl_wait();
         for (int e = lane; e < 16 * (HD / 8); e += 32) {
             const int r = e / (HD / 8), c = e % (HD / 8);
             const int gr = wrow0 + r;

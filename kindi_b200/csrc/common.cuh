@@ -64,6 +64,10 @@ __device__ __forceinline__ size_t kb_kv_offset(const KbCacheView& c, int page, i
 // barriers and tensor memory and fetch weights, which no kernel writes). The wait returns when the whole preceding
 // kernel has finished and its writes are visible, so results are those of strictly ordered launches; what is
 // gained is that launch latency and prologues overlap the predecessor's tail.
+// Before its wait a kernel also reads the step's metadata (positions, lengths, slots, row lists, the page table)
+// and cache pages of older positions. Callers therefore write those with operations that are complete before the
+// step's first kernel starts: the engine brings the page table up to date and then copies the metadata to the
+// device (a copy orders fully), and older pages were stored by earlier steps.
 __device__ __forceinline__ void kb_pdl_launch_now() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // Small grids (decode steps) let their successor start at once; large grids (prompt steps) do not: a successor that
 // was launched before its predecessor ended was measured to cost a prompt step several microseconds per kernel,

@@ -88,9 +88,8 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict_
     extern __shared__ float sv[];
     __shared__ float red[NORM_THREADS / 32];
     kb_pdl_launch();
-    kb_pdl_wait();
     const int r = blockIdx.x;
-    int t = rows ? rows[r] : r;
+    int t = rows ? rows[r] : r;                  // (the row list is step metadata, written before the step's kernels)
     if (t < 0 || t >= T) {
         if (threadIdx.x == 0) atomicOr(status, KB_ST_BAD_ROW);
         t = 0;
@@ -98,6 +97,43 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict_
     float* xr = x + (size_t)t * E;
     const float* dr = delta + (size_t)t * E;
     float ss = 0.0f;
+    if (VEC && E <= NORM_THREADS * 4) {
+        // the whole row in one pass, four elements a thread, kept in registers; the gains are fetched before the wait
+        // for the kernel that produces the row. Sums are those of the general form below.
+        const int i = threadIdx.x * 4;
+        float w4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (i < E) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) w4[c] = kb_to_f<TW>(w[i + c]);
+        }
+        kb_pdl_wait();
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < E) {
+            v = *(const float4*)(xr + i);
+            if (n_delta > 0) v = kb_sum_planes4(v, dr + i, n_delta, delta_stride);
+            if (write_back) *(float4*)(xr + i) = v;
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
+        ss = kb_warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = red[0];
+#pragma unroll
+        for (int k = 1; k < NORM_THREADS / 32; k++) tot += red[k];
+        const float scale = rsqrtf(tot / (float)E + eps);
+        if (i < E) {
+            TY* yr = y + (size_t)r * E + i;
+            yr[0] = kb_from_f<TY>(__fmul_rn(__fmul_rn(scale, v.x), w4[0]));
+            yr[1] = kb_from_f<TY>(__fmul_rn(__fmul_rn(scale, v.y), w4[1]));
+            yr[2] = kb_from_f<TY>(__fmul_rn(__fmul_rn(scale, v.z), w4[2]));
+            yr[3] = kb_from_f<TY>(__fmul_rn(__fmul_rn(scale, v.w), w4[3]));
+        }
+        return;
+    }
+    kb_pdl_wait();
     if (VEC) {
         for (int i = threadIdx.x * 4; i < E; i += NORM_THREADS * 4) {
             float4 v = *(const float4*)(xr + i);
@@ -389,7 +425,8 @@ __global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t pl
         const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
         int hd, KbCacheView cv, int* status) {
     kb_pdl_launch();
-    kb_pdl_wait();
+    // positions, slots and the page table were written before the step's first kernel: they are read, and the first
+    // angle of each thread is computed, before the wait for the kernel that produces the rows
     const int t = blockIdx.x, h = blockIdx.y;
     const int p = pos[t];
     const TIN* src = in + (size_t)t * ld_in + (size_t)h * hd;
@@ -421,10 +458,21 @@ __global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t pl
         return v;
     };
     const int half = rot / 2;
+    float c_first = 1.0f, sn_first = 0.0f;
+    if ((is_q || is_k) && (int)threadIdx.x < half) {
+        const float ang = __fmul_rn((float)p, inv_freq[threadIdx.x]);
+        c_first = cosf(ang);
+        sn_first = sinf(ang);
+    }
+    kb_pdl_wait();
     if (is_q || is_k) {
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float ang = __fmul_rn((float)p, inv_freq[i]);
-            const float c = cosf(ang), sn = sinf(ang);
+            float c = c_first, sn = sn_first;
+            if (i != (int)threadIdx.x) {
+                const float ang = __fmul_rn((float)p, inv_freq[i]);
+                c = cosf(ang);
+                sn = sinf(ang);
+            }
             const float a = rd(i), b = rd(i + half);
             dst[i] = kb_from_f<T>(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
             dst[i + half] = kb_from_f<T>(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn)));
