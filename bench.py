@@ -264,7 +264,7 @@ def main(argv=None) -> int:
         "clocks": clk,
         "gpu_launches": launches,
         "e2e": {"value": round(a.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": 4 * layout(a.batch, a.batch, a.batch)[1], "d2h_bytes_per_step": 4 * a.batch,
+                "h2d_bytes_per_step": 4 * layout(a.batch, a.batch, a.batch)[1], "d2h_bytes_per_step": 4 * a.batch + 4,
                 "ms_per_step": round(e2e_ms, 4)},
         "roofline": {"bound": "hbm", "achieved": round(bytes_step / dev_ms / 1e6, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(bytes_step / dev_ms / 1e6 / pk["hbm_gbs"], 4),

@@ -205,9 +205,28 @@ class Engine:
                            max_kv=ps.max_kv, dtype=self.dtype, device=self.device, status=self.status,
                            cache=self.cache, fast=self.dtype == torch.bfloat16)
 
+    def read_picked(self, picked: torch.Tensor) -> List[int]:
+        """the picked tokens of a step on the host, together with the status check: both are copied into one pinned
+        buffer and the host waits for the device once"""
+        n = picked.numel()
+        buf = getattr(self, "_host_out", None)
+        if buf is None or buf.numel() < n + 1:
+            buf = self._host_out = torch.empty(max(n + 1, self.max_batch + 1), dtype=torch.int32, pin_memory=True)
+        buf[:n].copy_(picked.view(-1), non_blocking=True)
+        buf[n:n + 1].copy_(self.status.view(-1), non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        out = buf[:n + 1].tolist()
+        if out[n]:
+            self._raise_status(out[n])
+        return out[:n]
+
     def check_status(self) -> None:
         """raise if a kernel of an earlier step met an index it had to skip (waits for the device)"""
         st = int(self.status.item())
+        if st:
+            self._raise_status(st)
+
+    def _raise_status(self, st: int) -> None:
         if st:
             self.status.zero_()
             what = [n for bit, n in ((K.ST_BAD_TOKEN, "a token id outside the vocabulary"),
@@ -322,9 +341,7 @@ class EngineStepper:
         from ..sampling.sampler import SequenceRandom
         if params.greedy and (params.repeat_penalty == 1.0 or histories is None):
             _, picked = self.engine.step(entries, greedy=True)
-            toks = picked.tolist()
-            self.engine.check_status()
-            return toks
+            return self.engine.read_picked(picked)
         logits = self.engine.step(entries)
         uniforms = None
         if not params.greedy:
@@ -334,6 +351,4 @@ class EngineStepper:
                     self._rng[sid] = SequenceRandom(self.seed, sid)
                 uniforms.append(self._rng[sid].next())
         picked = self.sampler.pick(logits, params, uniforms, histories if params.repeat_penalty != 1.0 else None)
-        toks = picked.tolist()
-        self.engine.check_status()
-        return toks
+        return self.engine.read_picked(picked)
