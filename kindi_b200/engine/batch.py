@@ -73,6 +73,16 @@ def pack(entries: Sequence[StepEntry], length_before: Sequence[int]) -> PackedSt
         q_start.append(q_start[-1] + n)
     R = len(rows)
     off, total = layout(T, B, R)
+    if T == B:
+        # one token each (a decode step, every step of a long generation): the buffer is put together as one list
+        kv_len = [n + 1 for n in length_before]
+        flat = [0] * total
+        for name, vals in (("tok", [e.tokens[0] for e in entries]), ("pos", list(length_before)), ("seq", range(B)),
+                           ("slot", slots), ("q_start", q_start), ("kv_len", kv_len), ("rows", rows)):
+            a, n = off[name]
+            flat[a:a + n] = vals
+        return PackedStep(T=T, B=B, R=R, meta=np.array(flat, dtype=np.int32), off=off, h_slot=tuple(slots),
+                          h_q_start=tuple(q_start), h_kv_len=tuple(kv_len), decode=True, max_q=1, max_kv=max(kv_len))
     meta = np.zeros(total, dtype=np.int32)
 
     def seg(name):

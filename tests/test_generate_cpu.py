@@ -124,6 +124,13 @@ def test_pack_arithmetic():
     assert seg("slot") == [3, 1] and seg("q_start") == [0, 3, 4] and seg("kv_len") == [13, 65]
     assert seg("rows") == [0, 2, 3] and (ps.T, ps.B, ps.R) == (4, 2, 3) and not ps.decode and ps.max_kv == 65
     assert pack([StepEntry(0, (1,), (0,)), StepEntry(2, (1,), (0,))], [5, 6]).decode
+    # one token each (the quick way through pack): the same segments, some sequences without a wanted place
+    ps = pack([StepEntry(4, (11,), (0,)), StepEntry(0, (12,), ()), StepEntry(9, (13,), (0,))], [7, 0, 200])
+    seg = lambda n: ps.meta[ps.off[n][0]: ps.off[n][0] + ps.off[n][1]].tolist()         # noqa: E731
+    assert seg("tok") == [11, 12, 13] and seg("pos") == [7, 0, 200] and seg("seq") == [0, 1, 2]
+    assert seg("slot") == [4, 0, 9] and seg("q_start") == [0, 1, 2, 3] and seg("kv_len") == [8, 1, 201]
+    assert seg("rows") == [0, 2] and (ps.T, ps.B, ps.R) == (3, 3, 2) and ps.decode and ps.max_kv == 201
+    assert ps.h_kv_len == (8, 1, 201) and ps.h_q_start == (0, 1, 2, 3) and ps.meta.dtype.name == "int32"
     assert layout(4, 2, 3) == layout(4, 2, 3) and all(a % 4 == 0 for a, _ in layout(5, 3, 2)[0].values())
     for bad in ([StepEntry(0, (), ())], [StepEntry(0, (1,), (1,))], [StepEntry(0, (1,)), StepEntry(0, (2,))], []):
         with pytest.raises(ValueError):
