@@ -1,6 +1,6 @@
 """Each part alone against its plain function; and that parts defined outside the package (a mixer with state of its
-own), a layer that runs twice and a layer that reads another layer's keys and values can be registered, built and
-stepped without a change to the package."""
+own, a feed-forward with routing, another position encoding), a layer that runs twice and a layer that reads another
+layer's keys and values can be registered, built and stepped without a change to the package."""
 import math
 
 import numpy as np
@@ -233,3 +233,127 @@ def test_toy_mixer_with_state_repeated_layer_and_shared_cache(tmp_path, dtype, t
             assert tiny.rel_err(mine, want[r]) < tol, (len(steps), r)
         eng.cache.check()
         assert eng.cache.slots.n_held == 0
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# a feed-forward with routing and another position encoding, both defined here. The feed-forward sends each row to
+# the one expert whose router logit (32-bit) is largest (ties: the lowest index) and returns relu(W1_e y) W2_e; it is
+# written with device-side PyTorch only and uses no host numbers, so the decode steps of a model that holds it are
+# still recorded. The position encoding rotates the first half of each head with frequencies 0.3 / (i + 1).
+def _toy_routed_parts():
+    from kindi_b200.config.registry import register_part
+    from kindi_b200.parts.base import Branch, FeedForward, PositionEncoding
+
+    class TopOneExperts(FeedForward):
+        @classmethod
+        def tensor_shapes(cls, spec, width):
+            n, f = int(spec["experts"]), int(spec["intermediate"])
+            out = {"router.weight": (n, width)}
+            for e in range(n):
+                out["experts.%d.w1.weight" % e] = (f, width)
+                out["experts.%d.w2.weight" % e] = (width, f)
+            return out
+
+        def __init__(self, spec, width, weights, *, dtype, device):
+            super().__init__(spec, width, weights, dtype=dtype, device=device)
+            n = int(spec["experts"])
+            self.router = weights("router.weight").float()
+            self.w1 = torch.stack([weights("experts.%d.w1.weight" % e).float() for e in range(n)])
+            self.w2 = torch.stack([weights("experts.%d.w2.weight" % e).float() for e in range(n)])
+
+        def forward(self, ctx, y):
+            yf = y.float()
+            pick = torch.argmax(yf @ self.router.T, dim=1)                    # ties: the first (lowest) index
+            h = torch.relu(torch.bmm(self.w1[pick], yf[:, :, None]))
+            return Branch(torch.bmm(self.w2[pick], h)[None, :, :, 0].contiguous())
+
+    class HarmonicRotation(PositionEncoding):
+        def __init__(self, spec, width, weights, *, dtype, device):
+            super().__init__(spec, width, weights, dtype=dtype, device=device)
+            self.rotary_dim = int(spec["rotary_dim"])
+            self.inv_freq = (0.3 / torch.arange(1, self.rotary_dim // 2 + 1, dtype=torch.float64)).float().to(device)
+
+    register_part("feed_forward", "toy_top1_experts", TopOneExperts, replace=True)
+    register_part("position", "toy_harmonic", HarmonicRotation, replace=True)
+
+
+def _toy_routed_spec(width=64, vocab=101):
+    from kindi_b200.config.spec import LayerSpec, ModelSpec, PartSpec, default_schedule
+    norm = PartSpec("rmsnorm", {"eps": 2e-6})
+    swiglu = PartSpec("swiglu", {"intermediate": 128})
+    routed = PartSpec("toy_top1_experts", {"experts": 3, "intermediate": 40})
+    att_h = PartSpec("attention", {"n_heads": 4, "n_kv_heads": 1, "head_dim": 16, "window": None,
+                                   "position": PartSpec("toy_harmonic", {"rotary_dim": 8})})
+    att_r = PartSpec("attention", {"n_heads": 4, "n_kv_heads": 1, "head_dim": 16, "window": None,
+                                   "position": PartSpec("rotary", {"base": 10000.0, "rotary_dim": 16})})
+    layers = (LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": att_h, "norm2": norm, "feed_forward": routed}), "a."),
+              LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": att_r, "norm2": norm, "feed_forward": swiglu}), "b."))
+    spec = ModelSpec(architecture="toy_routed", vocab_size=vocab, width=width, layers=layers,
+                     schedule=default_schedule(2), final_norm=norm, embedding_name="emb", final_norm_prefix="fn.",
+                     head_name="head")
+    spec.validate()
+    return spec
+
+
+def _toy_routed_plain(w, tokens, run_dtype):
+    """whole sequence, float64; the router sees the normalised row as the engine hands it over (rounded to the run
+    dtype), so that both pick the same expert"""
+    w = {k: v.double().cpu() for k, v in w.items()}
+    n = len(tokens)
+    x = P.embedding(w["emb"], tokens)
+    pos = torch.arange(n, dtype=torch.float32)
+    inv_h = (0.3 / torch.arange(1, 5, dtype=torch.float64)).float()
+    ang = (pos[:, None] * inv_h[None, :]).double()
+    tables = {"a.": (torch.cos(ang), torch.sin(ang)), "b.": P.rope_tables(torch.arange(n), 16, 10000.0, torch.float64)}
+    for p in ("a.", "b."):
+        cos, sin = tables[p]
+        y = P.rms_norm(x, w[p + "input_layernorm.weight"], 2e-6)
+        q = P.rope_rotate_half((y @ w[p + "self_attn.q_proj.weight"].T).view(n, 4, 16), cos, sin)
+        k = P.rope_rotate_half((y @ w[p + "self_attn.k_proj.weight"].T).view(n, 1, 16), cos, sin)
+        v = (y @ w[p + "self_attn.v_proj.weight"].T).view(n, 1, 16)
+        x = x + P.attention(q, k, v, 0.25).reshape(n, 64) @ w[p + "self_attn.o_proj.weight"].T
+        y = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 2e-6)
+        if p == "a.":
+            yr = y.to(run_dtype).double()
+            pick = torch.argmax((yr.float() @ w["a.mlp.router.weight"].float().T), dim=1)
+            out = torch.empty_like(x)
+            for t in range(n):
+                e = int(pick[t])
+                out[t] = w["a.mlp.experts.%d.w2.weight" % e] @ torch.relu(w["a.mlp.experts.%d.w1.weight" % e] @ yr[t])
+            x = x + out
+        else:
+            x = x + P.swiglu_mlp(y, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return P.rms_norm(x, w["fn.weight"], 2e-6) @ w["head"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 1.5e-2)])
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype, tol):
+    from kindi_b200.engine.engine import Engine
+    from kindi_b200.parts.model import expected_tensors
+    from kindi_b200.weights.random_init import random_tensors
+    _toy_routed_parts()
+    spec = _toy_routed_spec()
+    shapes = expected_tensors(spec)
+    assert shapes["a.mlp.router.weight"] == (3, 64) and shapes["a.mlp.experts.2.w2.weight"] == (64, 40)
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = random_tensors(shapes, seed=13, std=0.05, dtype=tdt)
+    # routing with wide margins, so that rounding cannot change an expert: token t carries a large value in feature
+    # t % 3 and the router reads exactly these three features (all three experts are used by every request)
+    w["emb"][:, :3] = 0
+    w["emb"][torch.arange(101), torch.arange(101) % 3] = 4.0
+    w["a.mlp.router.weight"].zero_()
+    w["a.mlp.router.weight"][torch.arange(3), torch.arange(3)] = 8.0
+    eng = Engine(spec=spec, tensors=w, ctx=1024, dtype=dtype, max_batch=3)
+    reqs = tiny.random_requests(101, [50, 9, 77, 2], seed=6)
+    want = {r: _toy_routed_plain(w, t, tdt).numpy() for r, t in reqs.items()}
+    for steps in (tiny.trace_whole(reqs), tiny.trace_last_n(reqs, 32), tiny.trace_batched(reqs, batch=3, decode=10)):
+        out = str(tmp_path / ("r%d" % len(steps)))
+        tiny.run_replay(eng, steps, out)
+        got = tiny.collect(out, steps, 101)
+        for r, t in reqs.items():
+            mine = np.stack([got[(r, i)] for i in range(len(t))])
+            assert tiny.rel_err(mine, want[r]) < tol, (len(steps), r)
+        eng.cache.check()
+        assert eng.cache.slots.n_held == 0
+    if eng.cuda_graphs:
+        assert eng.graph_replays > 0                  # its decode steps were recorded and replayed
