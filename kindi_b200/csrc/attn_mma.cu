@@ -10,6 +10,11 @@
 //   - decode form: the G rows of one token; the four warps split each page's 64 keys, gridDim.x splits the pages
 //     (kindi/nbq.cu:525-633: position splits and per-warp running maxima), and the parts are merged in a fixed order
 //     (kindi/nbq.cu:635-649).
+//   - decode form with rotation ("ROPE"): the kernel takes the 32-bit planes of the QKV product instead of finished
+//     queries. Every CTA sums and rotates the queries of its G heads itself (rotate-half pairs, the expressions of
+//     k_rope_store); the CTA whose pages hold the newest position also sums and rotates that position's key, takes its
+//     value, stores both in the cache for later steps and writes them into its shared-memory tile of the last page
+//     over what the TMA load brought. The rotate-and-store kernel and its round trip of Q through memory fall away.
 // Head sizes 64 and 128; any number of heads and groups for prefill, groups up to 16 for decode. Other shapes run
 // the general kernel.
 #include <stdio.h>
@@ -45,12 +50,58 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
 #ifndef AT_EARLY
 #define AT_EARLY 2                   // pages of older positions requested before the programmatic wait (decode form)
 #endif
-template <int HD, bool DEC>
+// what the decode form with rotation reads instead of finished queries
+struct AtRopeIn {
+    const float* planes;        // [n_planes][rows][ld]: the QKV product, a row = [q heads | k heads | v heads]
+    int n_planes;
+    size_t plane_stride;
+    int ld;
+    const float* inv_freq;      // [HD / 2]
+    bf16* pool;                 // the cache entry's pages, for the newest key and value; null: nothing is stored
+};
+// v[j][0..W-1] = sum over the planes, in order, of the W floats at p[j]: NS places at once, the loads of four planes of
+// all places in flight together (a chain of dependent round trips to the L2 would cost more than the kernel saved)
+template <int NS, int W>
+__device__ __forceinline__ void at_ld_sum(const float* const (&p)[NS], const bool (&on)[NS], int n_planes,
+                                          size_t plane_stride, float (&v)[NS][W]) {
+    auto ld = [](const float* q, float* o) {
+        if (W == 2) {
+            const float2 t = *(const float2*)q;
+            o[0] = t.x;
+            o[W - 1] = t.y;
+        } else {
+            o[0] = *q;
+        }
+    };
+#pragma unroll
+    for (int j = 0; j < NS; j++) {
+        v[j][0] = v[j][W - 1] = 0.0f;
+        if (on[j]) ld(p[j], v[j]);
+    }
+    for (int s0 = 1; s0 < n_planes; s0 += 4) {
+        float t[4][NS][W];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+#pragma unroll
+            for (int j = 0; j < NS; j++)
+                if (s0 + k < n_planes && on[j]) ld(p[j] + (size_t)(s0 + k) * plane_stride, t[k][j]);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+#pragma unroll
+            for (int j = 0; j < NS; j++)
+                if (s0 + k < n_planes && on[j]) {
+#pragma unroll
+                    for (int c = 0; c < W; c++) v[j][c] += t[k][j][c];
+                }
+    }
+}
+template <int HD, bool DEC, bool ROPE = false>
 __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constant__ CUtensorMap kvmap,
         const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
         float* __restrict__ part_ml, const int* __restrict__ slot, const int* __restrict__ q_start,
         const int* __restrict__ kv_len, int nh, int nkv, int G, float scale_log2e, int window,
-        const int* __restrict__ table, int table_stride, int n_pages, int* status) {
+        const int* __restrict__ table, int table_stride, int n_pages, int* status, AtRopeIn rp) {
+    static_assert(!ROPE || DEC, "rotation inside the kernel: decode form only");
     constexpr int AT_STAGES = DEC ? 3 : 2;      // pages in flight (two CTAs fit an SM in both forms)
     constexpr int KT = HD / 16;                 // k-steps of Q K^T
     constexpr int NT = DEC ? 2 : 8;             // 8-key tiles a warp takes from each page
@@ -119,7 +170,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
             for (int i = 0; i < n_iter; i++) {
                 const int s = i % AT_STAGES;
                 const uint32_t ph = (uint32_t)(i / AT_STAGES) & 1u;
-                if (DEC && !waited && (i >= AT_EARLY || pg_lo + i == (kvl - 1) / KB_PAGE)) {
+                // (with rotation and a key of its own the newest row is patched in shared memory, so its page may come early too)
+                if (DEC && !waited && (i >= AT_EARLY || (pg_lo + i == (kvl - 1) / KB_PAGE && !(ROPE && rp.pool)))) {
                     kb_pdl_wait();
                     waited = true;
                 }
@@ -146,6 +198,91 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         // this warp's 16 rows: r = wrow0 + 0..15; thread rows ra = lane / 4, rb = ra + 8
         const int wrow0 = row0 + (DEC ? 0 : warp * 16);
         bf16* qw = qs + (DEC ? 0 : warp) * 16 * QS;
+        constexpr int PPL = HD / 64;                 // pairs of the newest key a lane takes: i0 .. i0 + PPL - 1
+        constexpr int HALF = HD / 2;
+        const int i0 = lane * PPL;
+        const int tid = threadIdx.x;                 // 0..127 here: the consumer threads
+        float knew_lo[PPL], knew_hi[PPL], vnew[2][PPL];
+        const int p_new = kvl - 1;
+        const bool owns_new = ROPE && rp.pool != nullptr && p_new / KB_PAGE >= pg_lo && p_new / KB_PAGE <= pg_hi &&
+                              warp == (p_new % KB_PAGE) / 16;
+        if (ROPE) {
+            // Queries: pair e = tid + 128 k is (row e / HALF, pair e % HALF of the head) and 128 is a multiple of HALF,
+            // so a thread's pairs all have the same angle. Everything that does not come from the QKV product is
+            // done before the wait for it.
+            const float ang = __fmul_rn((float)p_new, rp.inv_freq[tid % HALF]);
+            const float qc = cosf(ang), qsn = sinf(ang);
+            float kc[PPL], ks[PPL];
+            int page_new = 0;
+            if (owns_new) {
+#pragma unroll
+                for (int j = 0; j < PPL; j++) {
+                    const float ak = __fmul_rn((float)p_new, rp.inv_freq[i0 + j]);
+                    kc[j] = cosf(ak);
+                    ks[j] = sinf(ak);
+                }
+                page_new = table[(size_t)slot[b] * table_stride + p_new / KB_PAGE];
+                if (page_new < 0 || page_new >= n_pages) page_new = -1;          // reported by the producer
+            }
+            // rows past G are zero
+            for (int e = G * (HD / 8) + tid; e < 16 * (HD / 8); e += 128)
+                *(uint4*)(qs + (e / (HD / 8)) * QS + (e % (HD / 8)) * 8) = make_uint4(0, 0, 0, 0);
+            kb_pdl_wait();
+            const float* prow = rp.planes + (size_t)qs0 * rp.ld;
+            const int n_pairs = G * HALF;
+            for (int e0 = tid; e0 < n_pairs; e0 += 4 * 128) {
+                const float* ptr[8];
+                bool on[8];
+                float val[8][1];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int e = e0 + 128 * k;
+                    on[2 * k] = on[2 * k + 1] = e < n_pairs;
+                    const int r = e / HALF, i = e % HALF;
+                    ptr[2 * k] = prow + (size_t)(hk * G + r) * HD + i;
+                    ptr[2 * k + 1] = ptr[2 * k] + HALF;
+                }
+                at_ld_sum<8, 1>(ptr, on, rp.n_planes, rp.plane_stride, val);
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int e = e0 + 128 * k;
+                    if (e < n_pairs) {
+                        const int r = e / HALF, i = e % HALF;
+                        const float a = val[2 * k][0], bb = val[2 * k + 1][0];
+                        qs[r * QS + i] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(a, qc), __fmul_rn(bb, qsn)));
+                        qs[r * QS + HALF + i] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(bb, qc), __fmul_rn(a, qsn)));
+                    }
+                }
+            }
+            if (owns_new) {
+                // the newest key (rotated) and value of this head: into the cache for later steps, and kept for the patch
+                const float* ksrc = prow + (size_t)(nh + hk) * HD, *vsrc = prow + (size_t)(nh + nkv + hk) * HD;
+                const float* ptr[4] = {ksrc + i0, ksrc + HALF + i0, vsrc + 2 * i0, vsrc + 2 * i0 + PPL};
+                const bool on[4] = {true, true, true, true};
+                float val[4][PPL];
+                at_ld_sum<4, PPL>(ptr, on, rp.n_planes, rp.plane_stride, val);
+#pragma unroll
+                for (int j = 0; j < PPL; j++) {
+                    knew_lo[j] = __fsub_rn(__fmul_rn(val[0][j], kc[j]), __fmul_rn(val[1][j], ks[j]));
+                    knew_hi[j] = __fadd_rn(__fmul_rn(val[1][j], kc[j]), __fmul_rn(val[0][j], ks[j]));
+                    vnew[0][j] = val[2][j];
+                    vnew[1][j] = val[3][j];
+                }
+                if (page_new >= 0) {
+                    const size_t base = (size_t)page_new * 2 * nkv;
+                    bf16* kd = rp.pool + ((base + hk) * KB_PAGE + p_new % KB_PAGE) * HD;
+                    bf16* vd = rp.pool + ((base + nkv + hk) * KB_PAGE + p_new % KB_PAGE) * HD;
+#pragma unroll
+                    for (int j = 0; j < PPL; j++) {
+                        kd[i0 + j] = __float2bfloat16_rn(knew_lo[j]);
+                        kd[HALF + i0 + j] = __float2bfloat16_rn(knew_hi[j]);
+                        vd[2 * i0 + j] = __float2bfloat16_rn(vnew[0][j]);
+                        vd[2 * i0 + PPL + j] = __float2bfloat16_rn(vnew[1][j]);
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");          // the four consumer warps: Q is whole
+        } else {
         if (DEC) kb_pdl_wait();
         for (int e = lane; e < 16 * (HD / 8); e += 32) {
             const int r = e / (HD / 8), c = e % (HD / 8);
@@ -158,6 +295,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
             *(uint4*)(qw + r * QS + c * 8) = v;
         }
         __syncwarp();
+        }
         uint32_t qf[KT][4];
 #pragma unroll
         for (int ks = 0; ks < KT; ks++) {
@@ -179,6 +317,24 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
             const int s = i % AT_STAGES;
             const uint32_t ph = (uint32_t)(i / AT_STAGES) & 1u;
             if (!mbar_wait(bar_full + s * 8, ph, status)) break;
+            if (ROPE && owns_new && pg_lo + i == p_new / KB_PAGE) {
+                // the newest position's row of this page: the values computed above, over what the load brought
+                uint8_t* kt8 = smem + s * STAGE_BYTES;
+                const int row = p_new % KB_PAGE;
+#pragma unroll
+                for (int j = 0; j < PPL; j++) {
+                    const int cl = i0 + j, ch = HALF + i0 + j;
+                    *(bf16*)(kt8 + tile_off(row, cl >> 3) + (cl & 7) * 2) = __float2bfloat16_rn(knew_lo[j]);
+                    *(bf16*)(kt8 + tile_off(row, ch >> 3) + (ch & 7) * 2) = __float2bfloat16_rn(knew_hi[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < 2 * PPL; j++) {
+                    const int c = 2 * i0 + j;
+                    *(bf16*)(kt8 + TILE_BYTES + tile_off(row, c >> 3) + (c & 7) * 2) =
+                        __float2bfloat16_rn(vnew[j / PPL][j % PPL]);
+                }
+                __syncwarp();
+            }
             const int key0 = (pg_lo + i) * KB_PAGE + kw0;           // absolute position of the warp's first key
             if (key0 <= wlast) {
                 const uint32_t kt = sbase + s * STAGE_BYTES, vt = kt + TILE_BYTES;
@@ -373,12 +529,12 @@ static int attn_smem_bytes() {
     return (body > merge ? body : merge) + 1024;
 }
 
-template <int HD, bool DEC>
+template <int HD, bool DEC, bool ROPE = false>
 static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, float* part_o,
                        float* part_ml, const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv,
                        float scale, int window, const int* table, int table_stride, int n_pages, int grid_x,
-                       int* status, cudaStream_t st) {
-    auto kern = k_attn_mma<HD, DEC>;
+                       int* status, cudaStream_t st, AtRopeIn rp = AtRopeIn()) {
+    auto kern = k_attn_mma<HD, DEC, ROPE>;
     const int sm = attn_smem_bytes<HD, DEC>();
     static bool done = false;
     if (!done) {
@@ -392,7 +548,7 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
     dim3 grid(grid_x, nkv, B);
     kb_launch(kern, grid, AT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, slot, q_start,
                                        kv_len, nh, nkv, nh / nkv, scale * 1.4426950408889634f, window, table,
-                                       table_stride, n_pages, status);
+                                       table_stride, n_pages, status, rp);
     return (int)cudaGetLastError();
 }
 
@@ -422,6 +578,44 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
 #undef AT_GO
     if (rc) return rc;
     if (decode && grid_x > 1) {
+        dim3 grid(nh, B);
+        kb_launch(k_attn_merge, grid, 4 * hd, 0, st, part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd);
+        return (int)cudaGetLastError();
+    }
+    return 0;
+}
+
+// Decode attention that rotates and stores by itself: qkv = the 32-bit planes [n_planes][rows][ld_qkv] of the QKV product
+// (a row = nh query heads, nkv key heads, nkv value heads of size hd), rotated over the whole head (rotary dimension =
+// hd) with inv_freq [hd / 2] at each sequence's newest position kv_len - 1. store != 0: the newest key and value go
+// into `pool` (the cache entry's own pages); store == 0: the entry reads another entry's pages and stores nothing.
+extern "C" int kb_attn_decode_rope(const float* qkv, int n_planes, long long plane_stride, int ld_qkv,
+                                   const float* inv_freq, void* out, int ldo, float* part_o, float* part_ml,
+                                   const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv,
+                                   int hd, float scale, int window, void* pool, int store, const int* table,
+                                   int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st) {
+    if (B <= 0 || grid_x <= 0) return 0;
+    if (grid_x > 64 || n_planes < 1) return (int)cudaErrorInvalidValue;
+    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 16) return (int)cudaErrorInvalidValue;
+    if ((ldo % 2) || (ld_qkv % 2) || (plane_stride % 2) || ((uintptr_t)qkv & 7)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map;
+    int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
+    if (rc) return rc;
+    AtRopeIn rp;
+    rp.planes = qkv;
+    rp.n_planes = n_planes;
+    rp.plane_stride = (size_t)plane_stride;
+    rp.ld = ld_qkv;
+    rp.inv_freq = inv_freq;
+    rp.pool = store ? (bf16*)pool : nullptr;
+    if (hd == 128)
+        rc = launch_attn<128, true, true>(map, nullptr, 0, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv,
+                                          scale, window, table, table_stride, n_pages, grid_x, status, st, rp);
+    else
+        rc = launch_attn<64, true, true>(map, nullptr, 0, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv,
+                                         scale, window, table, table_stride, n_pages, grid_x, status, st, rp);
+    if (rc) return rc;
+    if (grid_x > 1) {
         dim3 grid(nh, B);
         kb_launch(k_attn_merge, grid, 4 * hd, 0, st, part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd);
         return (int)cudaGetLastError();

@@ -122,9 +122,7 @@ def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages
         return False
     g = nh // nkv
     if ctx.decode and g <= 16:
-        # position splits: two CTAs fit an SM, so as many splits as fill one wave of 2 x 148 CTAs over all
-        # (sequence, key/value head) pairs, never more (a second, partly filled wave would cost a whole one)
-        splits = max(1, min(64, 2 * N_SM // (ctx.B * nkv)))
+        splits = decode_splits(ctx, nkv)
         K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table,
                    n_pages, decode=True, grid_x=splits, status=ctx.status)
         return True
@@ -137,6 +135,29 @@ def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages
         return True
     K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,
                decode=False, grid_x=-(-ctx.max_q * g // 64), status=ctx.status)
+    return True
+
+
+def decode_splits(ctx, nkv: int) -> int:
+    """position splits of a decode step: two CTAs fit an SM, so as many splits as fill one wave of 2 x SMs CTAs over
+    all (sequence, key/value head) pairs, never more (a second, partly filled wave would cost a whole one)"""
+    return max(1, min(64, 2 * N_SM // (ctx.B * nkv)))
+
+
+def attention_decode_rope(ctx, qkv, out, nh, nkv, hd, scale, window, inv_freq, rotary_dim, pool, store, table,
+                          n_pages) -> bool:
+    """a decode step's attention straight from the QKV planes (rotation and the store of the newest key and value
+    inside the attention kernel), where the kernel takes the shape; False: not taken"""
+    if ctx.B >= 32:
+        return False        # many rows: one pass of the row-wise rotate-and-store kernel costs less than every CTA's own sums
+    if not (ctx.decode and qkv.dim() == 3 and qkv.dtype == torch.float32 and hd in (64, 128) and rotary_dim == hd
+            and nh // nkv <= 16 and out.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16):
+        return False
+    if qkv.stride(2) != 1 or qkv.stride(1) != qkv.shape[2] or qkv.shape[2] % 2 or qkv.stride(0) % 2 \
+            or qkv.data_ptr() % 8 or out.stride(0) % 2:
+        return False
+    K.attn_decode_rope(qkv, inv_freq, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool,
+                       store, table, n_pages, grid_x=decode_splits(ctx, nkv), status=ctx.status)
     return True
 
 

@@ -44,6 +44,9 @@ _SIGS = {
     "kb_gemm_tc_splits": [c_int, c_int],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "kb_attn_decode_rope": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
+                            c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_attn_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_sample": [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
@@ -262,6 +265,28 @@ def attn_mma(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, 
                               table.stride(0), n_pages, 1 if decode else 0, grid_x, _p(status), _stream()),
            "attn_mma")
     if decode and grid_x > 1:
+        add_launches(1)         # the merge of the position splits
+
+
+def attn_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int,
+                     nh: int, nkv: int, hd: int, scale: float, window: int, pool: torch.Tensor, store: bool,
+                     table: torch.Tensor, n_pages: int, *, grid_x: int, status: torch.Tensor) -> None:
+    """decode attention that takes the QKV product as 32-bit planes [S, rows, (nh + 2 nkv) hd], rotates the queries
+    and the newest key over the whole head, stores the newest key and value (``store``) and attends; grid_x =
+    position splits"""
+    _need_cuda(qkv, out, pool, table, inv_freq)
+    assert qkv.dtype == torch.float32 and qkv.dim() == 3 and qkv.stride(2) == 1 and qkv.stride(1) == qkv.shape[2]
+    assert out.dtype == pool.dtype == torch.bfloat16 and out.stride(1) == 1 and pool.is_contiguous()
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == hd // 2
+    part_o = part_ml = None
+    if grid_x > 1:
+        part_o = torch.empty((B, nh, grid_x, hd), dtype=torch.float32, device=out.device)
+        part_ml = torch.empty((B, nh, grid_x, 2), dtype=torch.float32, device=out.device)
+    _check(load().kb_attn_decode_rope(_p(qkv), qkv.shape[0], qkv.stride(0), qkv.stride(1), _p(inv_freq), _p(out),
+                                      out.stride(0), _p(part_o), _p(part_ml), _p(slot), _p(q_start), _p(kv_len), B, nh,
+                                      nkv, hd, float(scale), int(window), _p(pool), 1 if store else 0, _p(table),
+                                      table.stride(0), n_pages, grid_x, _p(status), _stream()), "attn_decode_rope")
+    if grid_x > 1:
         add_launches(1)         # the merge of the position splits
 
 

@@ -70,11 +70,17 @@ class CausalSelfAttention(Mixer):
             qkv = L.rows_or_planes(ctx, y, self.wqkv, self.dtype)
             pool, table, n_pages = ctx.cache.kv_view(entry.cache)
             store_kv = nkv
+        att = torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
+        if ctx.fast and ctx.decode and qkv.dim() == 3 and not reads_other:
+            # a decode step: the attention kernel sums, rotates and stores by itself where it takes the shape
+            from ..kernels import fast
+            if fast.attention_decode_rope(ctx, qkv, att, nh, nkv, hd, self.scale, self.window, self.position.inv_freq,
+                                          self.position.rotary_dim, pool, True, table, n_pages):
+                return Branch(L.planes(ctx, att, self.wo))
         # 32-bit planes are summed, rotated and written out as rows; rows are rotated in place
         q = qkv if qkv.dim() == 2 else torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
         K.rope_store(qkv, q, self.position.inv_freq, self.position.rotary_dim, ctx.pos, ctx.seq, ctx.slot, nh,
                      store_kv, hd, pool if store_kv else None, table, n_pages, ctx.status)
-        att = torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
         from ..kernels import attention as A
         A.attention(ctx, q, att, nh, nkv, hd, self.scale, self.window, pool, table, n_pages)
         return Branch(L.planes(ctx, att, self.wo))

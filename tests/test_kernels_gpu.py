@@ -189,6 +189,49 @@ def test_attention_mma_decode(K, nh, nkv, hd, window):
     assert err < 1e-2
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,planes", [(20, 4, 128, 0, 5), (3, 1, 64, 0, 1), (16, 1, 128, 0, 2),
+                                                     (14, 2, 64, 100, 7), (10, 2, 128, 64, 3)])
+def test_attention_decode_rotates_and_stores_by_itself(K, nh, nkv, hd, window, planes):
+    """the decode attention that takes the QKV planes gives the same bits as the rotate-and-store kernel followed by
+    the decode attention, leaves the same cache behind, and without storing reads what is there"""
+    kv_lens = [1, 64, 65, 700, 129, 320, 128]
+    B = len(kv_lens)
+    pool, table, dense, slots, n_pages = _make_cache(kv_lens, nkv, hd, torch.bfloat16, seed=nh + hd)
+    g = torch.Generator(device="cpu").manual_seed(nh)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(B, width, generator=g)
+    parts = torch.randn(planes, B, width, generator=g)
+    parts[-1] = qkv - parts[:-1].sum(0)
+    parts = parts.cuda().contiguous()
+    inv = (250000.0 ** (-2 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().cuda()
+    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()      # noqa: E731
+    pos, seq, q_start = dev([n - 1 for n in kv_lens]), dev(list(range(B))), dev(list(range(B + 1)))
+    scale = 1.0 / math.sqrt(hd)
+    st = _status()
+    # the two kernels
+    pool_a = pool.clone()
+    q = torch.empty(B, nh * hd, dtype=torch.bfloat16, device="cuda")
+    K.rope_store(parts, q, inv, hd, pos, seq, slots, nh, nkv, hd, pool_a, table, n_pages, st)
+    want = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    K.attn_mma(q, want, slots, q_start, dev(kv_lens), B, nh, nkv, hd, scale, window, pool_a, table, n_pages,
+               decode=True, grid_x=5, status=st)
+    # the one kernel
+    pool_b = pool.clone()
+    got = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    K.attn_decode_rope(parts, inv, got, slots, q_start, dev(kv_lens), B, nh, nkv, hd, scale, window, pool_b, True,
+                       table, n_pages, grid_x=5, status=st)
+    assert int(st.item()) == 0
+    assert torch.equal(pool_a, pool_b)
+    assert torch.equal(got, want)
+    # nothing stored: the newest key and value are the ones the cache already holds
+    pool_c = pool_a.clone()
+    got2 = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    K.attn_decode_rope(parts[:, :, : nh * hd].contiguous(), inv, got2, slots, q_start, dev(kv_lens), B, nh, nkv, hd,
+                       scale, window, pool_c, False, table, n_pages, grid_x=3, status=st)
+    assert int(st.item()) == 0 and torch.equal(pool_c, pool_a)
+    assert _rel(got2.float(), want.float()) < 1e-2          # other splits: another order of the merge
+
+
 @pytest.mark.parametrize("M,F,K_,bn", [(129, 64, 128, 128), (2048, 1024, 520, 256), (300, 320, 264, 256), (200, 192, 72, 128)])
 def test_gemm_tc_finishes_swiglu_in_its_epilogue(K, M, F, K_, bn):
     g = torch.Generator(device="cuda").manual_seed(M + F + K_)
