@@ -3,6 +3,7 @@ run. Every function returns False / None when its kernel does not take the given
 general kernel instead; nothing here falls back to library code."""
 from __future__ import annotations
 
+import functools
 from typing import Optional
 
 import torch
@@ -33,6 +34,7 @@ def wants_planes(a: torch.Tensor, w: torch.Tensor) -> bool:
     return a.shape[0] <= SMALL_M and _tc_ok(a, w)
 
 
+@functools.lru_cache(maxsize=4096)
 def _splits_for(m: int, n: int, k: int, bn: int) -> int:
     """how many ways to split K for the persistent CTAs (one per SM). Estimated time of a launch, in microseconds:
     rounds of units times the K blocks of a unit (16 KB of weights each, at one SM's share of the memory bandwidth),
@@ -52,6 +54,7 @@ def _splits_for(m: int, n: int, k: int, bn: int) -> int:
     return best
 
 
+@functools.lru_cache(maxsize=4096)
 def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
     """(columns of a tile, row tiles per unit) for a prompt-sized product: the pair with the least estimated time.
     A K block of a unit costs what is slower, its MMAs (0.276 us for 128 x 256 x 64) or bringing its operand tiles
