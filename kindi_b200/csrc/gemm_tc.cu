@@ -22,14 +22,18 @@
 #endif
 #define TC_THREADS 192          // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 
-template <int BN, int STAGES, int MT = 1>
+template <int BN, int STAGES, int MT = 1, bool SWAP = false>
 struct TcSmem {
     static constexpr int A_BYTES = MT * TC_BM * TC_BK * 2;
     static constexpr int B_BYTES = BN * TC_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+    // prefill form: 4 KB per epilogue warp, where 32 rows of the accumulator are turned into whole 128-byte row pieces
+    static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
+    static constexpr int EPI_BYTES = SWAP ? 0 : 4 * 4096;
+    static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
     static constexpr int N_BARS = 2 * STAGES + 4;
     static constexpr int TOTAL = BAR_OFF + N_BARS * 8 + 16 + 1024;     // + alignment slack
+    static_assert(TOTAL <= 227 * 1024, "shared memory of a CTA");
 };
 
 // MT = 2 (prefill form only): a unit is TWO 128-row tiles of the same BN columns, so one weight tile in shared memory
@@ -39,7 +43,7 @@ template <int BN, int STAGES, bool SWAP, typename TC, int MT = 1>
 __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ CUtensorMap mapP,
         const __grid_constant__ CUtensorMap mapQ, TC* __restrict__ C, int rowsP, int rowsQ, int K, int ldc,
         long long split_stride, int kb_per_split, int n_splits, int* status, int swiglu_ld) {
-    using S = TcSmem<BN, STAGES, MT>;
+    using S = TcSmem<BN, STAGES, MT, SWAP>;
     static_assert(MT == 1 || (!SWAP && 2 * BN <= 512), "two row tiles: prefill form, both accumulators in tensor memory");
     extern __shared__ uint8_t smem_raw[];
     if (SWAP) kb_pdl_launch_now();               // decode steps only (see common.cuh)
@@ -204,46 +208,78 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                         *(uint4*)(dst + 8) = make_uint4(h[4], h[5], h[6], h[7]);
                     }
                 }
+            } else if (!SWAP) {
+                // C[token][feature]: a thread holds one row of the accumulator. The warp's 32 rows x 128 bytes go through
+                // its staging area (16-byte pieces, swizzled by the row so that neither side meets bank conflicts) and
+                // leave as whole 128-byte pieces of four rows per store instruction.
+                constexpr int CW = 128 / (int)sizeof(TC);            // columns per pass: 32 (float) or 64 (bf16)
+                constexpr int PW = 16 / (int)sizeof(TC);             // columns per 16-byte piece
+                uint8_t* stg = smem + S::EPI_OFF + quarter * 4096;
+                const bool vec_ok = (((uintptr_t)Cz) & 15) == 0 && (ldc % PW) == 0;
+                const int myrow = lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += CW) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tbase + c0, r);
+                    tmem_ld_wait();
+                    if (sizeof(TC) == 4) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            *(uint4*)(stg + myrow * 128 + ((j ^ (myrow & 7)) << 4)) =
+                                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int half = 0; half < 2; half++) {
+                            if (half == 1) {
+                                tmem_ld_32x32(tbase + c0 + 32, r);       // (columns past the accumulator are never stored)
+                                tmem_ld_wait();
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint32_t h[4];
+#pragma unroll
+                                for (int c = 0; c < 4; c++) {
+                                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * c]),
+                                                                             __uint_as_float(r[8 * j + 2 * c + 1]));
+                                    h[c] = *(uint32_t*)&v;
+                                }
+                                *(uint4*)(stg + myrow * 128 + (((half * 4 + j) ^ (myrow & 7)) << 4)) =
+                                    make_uint4(h[0], h[1], h[2], h[3]);
+                            }
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int rr = i * 4 + (lane >> 3), jj = lane & 7;
+                        const uint4 v = *(const uint4*)(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
+                        const int grow = p0 + quarter * 32 + rr, ct = c0 + jj * PW, gcol = q0 + ct;
+                        if (grow < rowsP && ct < BN && gcol < rowsQ) {
+                            TC* dst = Cz + (size_t)grow * ldc + gcol;
+                            if (vec_ok && gcol + PW <= rowsQ) {
+                                *(uint4*)dst = v;
+                            } else {
+                                const TC* e = (const TC*)&v;
+#pragma unroll
+                                for (int c = 0; c < PW; c++)
+                                    if (gcol + c < rowsQ) dst[c] = e[c];
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
             } else
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
+                // C[token q0 + c][feature prow]: a warp's 32 lanes write 32 consecutive features
                 uint32_t r[16];
                 tmem_ld_32x16(tbase + c0, r);
                 tmem_ld_wait();
-                if (SWAP) {
-                    // C[token q0 + c][feature prow]: a warp's 32 lanes write 32 consecutive features
-                    if (prow < rowsP) {
+                if (prow < rowsP) {
 #pragma unroll
-                        for (int c = 0; c < 16; c++)
-                            if (q0 + c0 + c < rowsQ)
-                                Cz[(size_t)(q0 + c0 + c) * ldc + prow] = kb_from_f<TC>(__uint_as_float(r[c]));
-                    }
-                } else {
-                    // C[token prow][feature q0 + c]: each thread writes 16 consecutive features of its row
-                    if (prow < rowsP) {
-                        TC* dst = Cz + (size_t)prow * ldc + q0 + c0;
-                        if (q0 + c0 + 16 <= rowsQ && (((uintptr_t)dst) & 15) == 0) {
-                            if (sizeof(TC) == 4) {
-#pragma unroll
-                                for (int c = 0; c < 16; c += 4)
-                                    *(uint4*)(dst + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
-                            } else {
-                                uint32_t h[8];
-#pragma unroll
-                                for (int c = 0; c < 8; c++) {
-                                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * c]),
-                                                                             __uint_as_float(r[2 * c + 1]));
-                                    h[c] = *(uint32_t*)&v;
-                                }
-                                *(uint4*)(dst) = make_uint4(h[0], h[1], h[2], h[3]);
-                                *(uint4*)(dst + 8) = make_uint4(h[4], h[5], h[6], h[7]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < 16; c++)
-                                if (q0 + c0 + c < rowsQ) dst[c] = kb_from_f<TC>(__uint_as_float(r[c]));
-                        }
-                    }
+                    for (int c = 0; c < 16; c++)
+                        if (q0 + c0 + c < rowsQ)
+                            Cz[(size_t)(q0 + c0 + c) * ldc + prow] = kb_from_f<TC>(__uint_as_float(r[c]));
                 }
             }
             }
@@ -274,7 +310,7 @@ static int kb_sm_count() {
 template <int BN, int STAGES, bool SWAP, typename TC, int MT = 1>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int rowsP, int rowsQ, int K, int ldc,
                      int splits, long long split_stride, int* status, cudaStream_t st, int swiglu_ld) {
-    using S = TcSmem<BN, STAGES, MT>;
+    using S = TcSmem<BN, STAGES, MT, SWAP>;
     auto kern = k_gemm_tc<BN, STAGES, SWAP, TC, MT>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -343,9 +379,13 @@ extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int
                : launch_tc<BN, ST, false, bf16, 2>(mp, mq, C, rowsP, rowsQ, K, ldc, splits, split_stride, status, st, swiglu_ld)
         switch (bn) {
             case 128: TC_GO2(128, 4);
+            case 144: TC_GO2(144, 4);
             case 160: TC_GO2(160, 4);
+            case 176: TC_GO2(176, 3);
             case 192: TC_GO2(192, 3);
+            case 208: TC_GO2(208, 3);
             case 224: TC_GO2(224, 3);
+            case 240: TC_GO2(240, 3);
             case 256: TC_GO2(256, 3);
             default: return (int)cudaErrorInvalidValue;
         }
@@ -354,9 +394,13 @@ extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int
         switch (bn) {
             case 64: TC_GO(64, 6, false);
             case 128: TC_GO(128, 6, false);
+            case 144: TC_GO(144, 6, false);
             case 160: TC_GO(160, 5, false);
+            case 176: TC_GO(176, 5, false);
             case 192: TC_GO(192, 5, false);
+            case 208: TC_GO(208, 4, false);
             case 224: TC_GO(224, 4, false);
+            case 240: TC_GO(240, 4, false);
             case 256: TC_GO(256, 4, false);
             default: return (int)cudaErrorInvalidValue;
         }

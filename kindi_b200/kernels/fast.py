@@ -66,7 +66,7 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
     kb = -(-k // 64)
     best, best_cost = (128, 1), None
     for mt in ((1, 2) if m >= 256 else (1,)):
-        for bn in (256, 224, 192, 160, 128):
+        for bn in (256, 240, 224, 208, 192, 176, 160, 144, 128):
             if swiglu and bn not in (128, 256):
                 continue
             units = -(-m // (128 * mt)) * -(-n // bn)

@@ -41,6 +41,8 @@ TC_CASES = [
     (128, 256, 64, False, 256, 1), (128, 128, 128, False, 128, 1), (200, 300, 136, False, 128, 1),
     (2048, 512, 2560, False, 256, 1), (130, 72, 72, False, 64, 1), (257, 1000, 520, False, 256, 1),
     (300, 700, 200, False, 160, 1), (129, 500, 136, False, 192, 1), (512, 2560, 320, False, 224, 1),
+    (260, 2560, 200, False, 144, 1), (140, 360, 72, False, 176, 1), (300, 3584, 264, False, 208, 1),
+    (129, 1000, 136, False, 240, 1),
     (1, 128, 64, True, 16, 1), (8, 384, 2560, True, 16, 1), (8, 384, 2560, True, 16, 5), (17, 200, 264, True, 32, 3),
     (64, 331 * 8, 1096, True, 64, 4), (100, 256, 4096, True, 128, 8), (5, 130, 72, True, 16, 2),
 ]
@@ -273,7 +275,8 @@ def test_attention_tc_prefill(K, nh, nkv, window):
 
 
 @pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 128), (2048, 2560, 1096, 160), (300, 700, 200, 192),
-                                       (513, 1000, 136, 224), (1000, 520, 264, 256)])
+                                       (513, 1000, 136, 224), (1000, 520, 264, 256), (2048, 2560, 328, 144),
+                                       (300, 400, 72, 176), (2048, 3584, 200, 208), (257, 500, 136, 240)])
 def test_gemm_tc_two_row_tiles(K, M, N, K_, bn):
     g = torch.Generator(device="cuda").manual_seed(M + N + K_)
     a = torch.randn(M, K_, device="cuda", generator=g).to(torch.bfloat16)
