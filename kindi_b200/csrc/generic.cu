@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* __restrict__
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
     kb_pdl_launch();
     kb_pdl_wait();
-    const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     float* xr = x + (size_t)t * E;
     const float* dr = delta + (size_t)t * E;
@@ -294,13 +294,17 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
     cudaError_t e = cudaSuccess;
     if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= 512 && (write_back || n_delta == 0) &&
         (((uintptr_t)y) % 8) == 0) {
+// rows (warps) per block (1, 2 and 4 were measured slower on a 2048-row step)
+#ifndef NORM_RW
+#define NORM_RW 8
+#endif
 #define KB_NORM_REGS(NCH)                                                                                          \
     do {                                                                                                           \
         if (wdtype == KB_F32)                                                                                      \
-            e = kb_launch(k_add_rmsnorm_regs<float, NCH>, (T + 7) / 8, 256, 0, st, x, delta, n_delta,              \
+            e = kb_launch(k_add_rmsnorm_regs<float, NCH>, (T + NORM_RW - 1) / NORM_RW, 32 * NORM_RW, 0, st, x, delta, n_delta, \
                           (size_t)delta_stride, (const float*)w, eps, (bf16*)y, T, E);                             \
         else                                                                                                       \
-            e = kb_launch(k_add_rmsnorm_regs<bf16, NCH>, (T + 7) / 8, 256, 0, st, x, delta, n_delta,               \
+            e = kb_launch(k_add_rmsnorm_regs<bf16, NCH>, (T + NORM_RW - 1) / NORM_RW, 32 * NORM_RW, 0, st, x, delta, n_delta, \
                           (size_t)delta_stride, (const bf16*)w, eps, (bf16*)y, T, E);                              \
         return (int)e;                                                                                             \
     } while (0)
