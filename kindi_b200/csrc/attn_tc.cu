@@ -67,17 +67,22 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
     const uint32_t sbase = smem_u32(smem);
     const uint32_t s_q = sbase, s_kv = s_q + FT_Q_BYTES, s_p = s_kv + FT_STAGES * FT_STAGE_BYTES;
     const uint32_t bars = s_p + FT_P_BYTES;
-    const uint32_t b_kv_full = bars, b_kv_empty = b_kv_full + FT_STAGES * 8, b_s_full = b_kv_empty + FT_STAGES * 8;
+    // keys and values of a stage have barriers of their own: a stage's key tile is free as soon as Q K^T of its page
+    // is done, long before P V of that page frees the value tile, so the next keys are on their way a page earlier
+    const uint32_t b_k_full = bars, b_k_empty = b_k_full + FT_STAGES * 8, b_v_full = b_k_empty + FT_STAGES * 8;
+    const uint32_t b_v_empty = b_v_full + FT_STAGES * 8, b_s_full = b_v_empty + FT_STAGES * 8;
     const uint32_t b_s_free = b_s_full + 16, b_p_ready = b_s_free + 16, b_p_free = b_p_ready + 8;
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + FT_P_BYTES +
-                                                        (2 * FT_STAGES + 6) * 8);
+                                                        (4 * FT_STAGES + 6) * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, hk = blockIdx.y;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < FT_STAGES; s++) {
-            mbar_init(b_kv_full + s * 8, 1);
-            mbar_init(b_kv_empty + s * 8, 1);
+            mbar_init(b_k_full + s * 8, 1);
+            mbar_init(b_k_empty + s * 8, 1);
+            mbar_init(b_v_full + s * 8, 1);
+            mbar_init(b_v_empty + s * 8, 1);
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(b_s_full + i * 8, 1);
@@ -128,22 +133,53 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
         // ------------------------------------------------------------ TMA producer
         if (lane == 0 && n_iter > 0) {
             const int* trow = table + (size_t)slot[b] * table_stride;
-            for (int i = 0; i < n_iter; i++) {
-                const int s = i % FT_STAGES;
-                const uint32_t ph = (uint32_t)(i / FT_STAGES) & 1u;
-                if (!mbar_wait(b_kv_empty + s * 8, ph ^ 1u, status)) break;
+            // two streams, keys and values, each held back only by its own tiles; one thread polls both
+            auto page_of = [&](int i) {
                 int page = trow[pg_lo + i];
                 if (page < 0 || page >= n_pages) {
                     atomicOr(status, KB_ST_BAD_PAGE);
                     page = 0;
                 }
-                mbar_expect_tx(b_kv_full + s * 8, FT_STAGE_BYTES);
-                const uint32_t dst = s_kv + s * FT_STAGE_BYTES;
-                const int krow = ((page * 2 + 0) * nkv + hk) * KB_PAGE, vrow = ((page * 2 + 1) * nkv + hk) * KB_PAGE;
-                tma_load_2d(dst, &kvmap, 0, krow, b_kv_full + s * 8);
-                tma_load_2d(dst + 8192, &kvmap, 64, krow, b_kv_full + s * 8);
-                tma_load_2d(dst + FT_TILE_BYTES, &kvmap, 0, vrow, b_kv_full + s * 8);
-                tma_load_2d(dst + FT_TILE_BYTES + 8192, &kvmap, 64, vrow, b_kv_full + s * 8);
+                return page;
+            };
+            int ik = 0, iv = 0, spins = 0;
+            uint64_t t0 = kb_globaltimer();
+            while (iv < n_iter) {
+                bool moved = false;
+                if (ik < n_iter) {
+                    const int s = ik % FT_STAGES;
+                    if (mbar_poll(b_k_empty + s * 8, ((uint32_t)(ik / FT_STAGES) & 1u) ^ 1u)) {
+                        const int krow = ((page_of(ik) * 2 + 0) * nkv + hk) * KB_PAGE;
+                        const uint32_t dst = s_kv + s * FT_STAGE_BYTES;
+                        mbar_expect_tx(b_k_full + s * 8, FT_TILE_BYTES);
+                        tma_load_2d(dst, &kvmap, 0, krow, b_k_full + s * 8);
+                        tma_load_2d(dst + 8192, &kvmap, 64, krow, b_k_full + s * 8);
+                        ik++;
+                        moved = true;
+                    }
+                }
+                if (iv < ik) {
+                    const int s = iv % FT_STAGES;
+                    if (mbar_poll(b_v_empty + s * 8, ((uint32_t)(iv / FT_STAGES) & 1u) ^ 1u)) {
+                        const int vrow = ((page_of(iv) * 2 + 1) * nkv + hk) * KB_PAGE;
+                        const uint32_t dst = s_kv + s * FT_STAGE_BYTES + FT_TILE_BYTES;
+                        mbar_expect_tx(b_v_full + s * 8, FT_TILE_BYTES);
+                        tma_load_2d(dst, &kvmap, 0, vrow, b_v_full + s * 8);
+                        tma_load_2d(dst + 8192, &kvmap, 64, vrow, b_v_full + s * 8);
+                        iv++;
+                        moved = true;
+                    }
+                }
+                if (moved) {
+                    spins = 0;
+                } else if (++spins >= 256) {
+                    // nothing moved for a while: look at the clock (the limit of every wait of this library)
+                    if (spins == 256) t0 = kb_globaltimer();
+                    else if ((spins & 255) == 0 && kb_globaltimer() - t0 > KB_WAIT_NS) {
+                        atomicOr(status, KB_ST_WAIT_TIMEOUT);
+                        break;
+                    }
+                }
             }
         }
     } else if (warp == 5) {
@@ -161,8 +197,9 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                     umma_bf16(d, umma_desc_sw128(s_q + (k >> 2) * 16384 + (k & 3) * 32),
                               umma_desc_sw128(kt + (k >> 2) * 8192 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(b_s_full + (j & 1) * 8);
+                umma_commit(b_k_empty + s * 8);                   // the stage's keys have been read
             };
-            ok = mbar_wait(b_kv_full, 0, status);
+            ok = mbar_wait(b_k_full, 0, status);
             if (ok) {
                 tc_fence_after();
                 issue_s(0);
@@ -170,13 +207,14 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             for (int j = 0; j < n_iter && ok; j++) {
                 if (j + 1 < n_iter) {
                     const int s1 = (j + 1) % FT_STAGES;
-                    if (!(ok = mbar_wait(b_kv_full + s1 * 8, (uint32_t)((j + 1) / FT_STAGES) & 1u, status))) break;
+                    if (!(ok = mbar_wait(b_k_full + s1 * 8, (uint32_t)((j + 1) / FT_STAGES) & 1u, status))) break;
                     // S buffer (j + 1) & 1 was last read for page j - 1
                     if (j >= 1 && !(ok = mbar_wait(b_s_free + ((j + 1) & 1) * 8, (uint32_t)((j - 1) >> 1) & 1u, status))) break;
                     tc_fence_after();
                     issue_s(j + 1);
                 }
                 if (!(ok = mbar_wait(b_p_ready, (uint32_t)j & 1u, status))) break;
+                if (!(ok = mbar_wait(b_v_full + (j % FT_STAGES) * 8, (uint32_t)(j / FT_STAGES) & 1u, status))) break;
                 tc_fence_after();
                 const uint32_t pt = s_p;
                 const uint32_t vt = s_kv + (j % FT_STAGES) * FT_STAGE_BYTES + FT_TILE_BYTES;
@@ -185,7 +223,7 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                     umma_bf16(t_o, umma_desc_sw128(pt + k * 32), umma_desc_mn_sw128(vt + k * 2048, 8192), idesc_o,
                               (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(b_p_free);                            // P buffer free; O holds pages 0..j
-                umma_commit(b_kv_empty + (j % FT_STAGES) * 8);    // the stage's K and V have been read
+                umma_commit(b_v_empty + (j % FT_STAGES) * 8);     // the stage's values have been read
             }
         }
     } else if (n_iter > 0) {
@@ -217,20 +255,20 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                 // the whole page lies inside this row's span (all pages but the last one or two): no masks
 #pragma unroll
                 for (int c = 0; c < 64; c++) {
-                    const float s = __uint_as_float(sv[c]) * scale_log2e;
-                    sv[c] = __float_as_uint(s);
-                    mx4[c & 3] = fmaxf(mx4[c & 3], s);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
                 }
             } else {
 #pragma unroll
                 for (int c = 0; c < 64; c++) {
                     const int p = key0 + c;
-                    const float s = (p <= p_row && p >= lo_row) ? __uint_as_float(sv[c]) * scale_log2e : -INFINITY;
+                    const float s = (p <= p_row && p >= lo_row) ? __uint_as_float(sv[c]) : -INFINITY;
                     sv[c] = __float_as_uint(s);
                     mx4[c & 3] = fmaxf(mx4[c & 3], s);
                 }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // (the scores stay as the product left them; the scale, which is positive, is applied to the maximum here
+            // and to each score inside the exponent's one multiply-add)
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;
             // lazy reference: move it only when the maximum has grown by more than FT_LAZY
             const bool grow = mx > m_ref + FT_LAZY || (m_ref == -INFINITY && mx > -INFINITY);
             float f = 1.0f;
@@ -266,8 +304,8 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                 uint32_t h[4];
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    const float p0 = ft_exp2(__uint_as_float(sv[c8 * 8 + 2 * c]) - mr);
-                    const float p1 = ft_exp2(__uint_as_float(sv[c8 * 8 + 2 * c + 1]) - mr);
+                    const float p0 = ft_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * c]), scale_log2e, -mr));
+                    const float p1 = ft_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * c + 1]), scale_log2e, -mr));
                     sum4[c] += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                     h[c] = *(uint32_t*)&v;
@@ -327,7 +365,7 @@ extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int*
     int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
     if (rc) return rc;
     // 112 KB of tiles + barriers + what aligning the base to 1024 can cost when it is aligned to 128: two CTAs fit
-    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + FT_P_BYTES + 128 + 896;
+    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + FT_P_BYTES + 256 + 768;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(k_attn_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);

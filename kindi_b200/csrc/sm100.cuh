@@ -39,6 +39,16 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// has the phase with the given parity completed? (returns at once)
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // wait for the phase with the given parity to complete; false (and the status bit) when the time runs out
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
     if (mbar_test(bar, parity)) return true;
