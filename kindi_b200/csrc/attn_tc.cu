@@ -6,11 +6,15 @@
 // Warps 0-3 (one thread per row) do the softmax, warp 4 brings pages of 64 positions in by TMA (two 64-column tile
 // loads per 128-wide head for K and for V, 128-byte swizzle, no multicast), one thread of warp 5 issues the MMAs:
 //     S[j % 2] = Q K_j^T      M 128 x N 64 x K 128: Q and K both K-major in shared memory
-//     O       += P_j V_j      M 128 x N 128 x K 64: P K-major (written by the softmax threads), V as stored in the cache,
-//                              i.e. MN-major
-// S has two buffers in tensor memory so that Q K^T of the next page runs while the softmax of this one does; P has one
-// buffer in shared memory (P V of a page is long done when the next page's probabilities are ready). A CTA needs 112 KB
-// of shared memory and 256 columns of tensor memory, so two CTAs share an SM and one's softmax hides the other's waits. The running maximum is applied lazily: the exponent's reference only moves (and O in tensor
+//     O       += P_j V_j      M 128 x N 128 x K 64: P from TENSOR memory (the A operand), V as stored in the cache,
+//                              i.e. MN-major, from shared memory
+// S has two buffers in tensor memory so that Q K^T of the next page runs while the softmax of this one does. A softmax
+// thread reads its row of S, and writes the row's probabilities back as bf16 pairs over the first 32 columns of the
+// same buffer, from where P V reads them: P never passes through shared memory. The tensor pipe runs the products in
+// the order of their issue (S_{j+1}, P V_j, S_{j+2}, ...), which is all the ordering the two buffers need.
+// Key and value tiles of a stage are freed separately (keys as soon as Q K^T of the page is done). A CTA needs 96 KB
+// of shared memory and 256 columns of tensor memory, so two CTAs share an SM and one's softmax hides the other's
+// waits. The running maximum is applied lazily: the exponent's reference only moves (and O in tensor
 // memory is only rescaled, by tcgen05.ld / tcgen05.st) when a row's maximum has grown by more than 8 (a factor 256 in
 // the probabilities, which bf16 and the 32-bit sums hold without loss); the final division by the row sum makes the
 // result the same as with an exact running maximum (kindi/nbq_fa.cu:31-151 is the recurrence this follows).
@@ -23,7 +27,6 @@
 #define FT_TILE_BYTES (64 * FT_HD * 2)           // one page of keys (or values) of one head: 16 KB
 #define FT_STAGE_BYTES (2 * FT_TILE_BYTES)
 #define FT_Q_BYTES (128 * FT_HD * 2)             // 32 KB: two K-blocks of [128 rows][64 columns]
-#define FT_P_BYTES (128 * 64 * 2)                // 16 KB
 #define FT_LAZY 8.0f
 
 __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) { tmem_ld_32x32(taddr, r); }
@@ -65,15 +68,15 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t s_q = sbase, s_kv = s_q + FT_Q_BYTES, s_p = s_kv + FT_STAGES * FT_STAGE_BYTES;
-    const uint32_t bars = s_p + FT_P_BYTES;
+    const uint32_t s_q = sbase, s_kv = s_q + FT_Q_BYTES;
+    const uint32_t bars = s_kv + FT_STAGES * FT_STAGE_BYTES;
     // keys and values of a stage have barriers of their own: a stage's key tile is free as soon as Q K^T of its page
     // is done, long before P V of that page frees the value tile, so the next keys are on their way a page earlier
     const uint32_t b_k_full = bars, b_k_empty = b_k_full + FT_STAGES * 8, b_v_full = b_k_empty + FT_STAGES * 8;
     const uint32_t b_v_empty = b_v_full + FT_STAGES * 8, b_s_full = b_v_empty + FT_STAGES * 8;
-    const uint32_t b_s_free = b_s_full + 16, b_p_ready = b_s_free + 16, b_p_free = b_p_ready + 8;
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + FT_P_BYTES +
-                                                        (4 * FT_STAGES + 6) * 8);
+    const uint32_t b_p_ready = b_s_full + 16, b_pv_done = b_p_ready + 8;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES +
+                                                        (4 * FT_STAGES + 4) * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, hk = blockIdx.y;
 
@@ -84,12 +87,9 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             mbar_init(b_v_full + s * 8, 1);
             mbar_init(b_v_empty + s * 8, 1);
         }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(b_s_full + i * 8, 1);
-            mbar_init(b_s_free + i * 8, 4);
-        }
+        for (int i = 0; i < 2; i++) mbar_init(b_s_full + i * 8, 1);
         mbar_init(b_p_ready, 4);
-        mbar_init(b_p_free, 1);
+        mbar_init(b_pv_done, 1);
         mbar_fence_init();
         tma_prefetch_desc(&kvmap);
     }
@@ -172,7 +172,10 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                 }
                 if (moved) {
                     spins = 0;
-                } else if (++spins >= 256) {
+                    continue;
+                }
+                __nanosleep(100);                    // an idle poller would take issue slots from the softmax warp beside it
+                if (++spins >= 256) {
                     // nothing moved for a while: look at the clock (the limit of every wait of this library)
                     if (spins == 256) t0 = kb_globaltimer();
                     else if ((spins & 255) == 0 && kb_globaltimer() - t0 > KB_WAIT_NS) {
@@ -208,21 +211,21 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                 if (j + 1 < n_iter) {
                     const int s1 = (j + 1) % FT_STAGES;
                     if (!(ok = mbar_wait(b_k_full + s1 * 8, (uint32_t)((j + 1) / FT_STAGES) & 1u, status))) break;
-                    // S buffer (j + 1) & 1 was last read for page j - 1
-                    if (j >= 1 && !(ok = mbar_wait(b_s_free + ((j + 1) & 1) * 8, (uint32_t)((j - 1) >> 1) & 1u, status))) break;
+                    // S buffer (j + 1) & 1 holds P of page j - 1, which P V of page j - 1, issued before this product,
+                    // reads: the tensor pipe runs them in order, and the softmax threads were done with the buffer when
+                    // they handed that P over
                     tc_fence_after();
                     issue_s(j + 1);
                 }
                 if (!(ok = mbar_wait(b_p_ready, (uint32_t)j & 1u, status))) break;
                 if (!(ok = mbar_wait(b_v_full + (j % FT_STAGES) * 8, (uint32_t)(j / FT_STAGES) & 1u, status))) break;
                 tc_fence_after();
-                const uint32_t pt = s_p;
                 const uint32_t vt = s_kv + (j % FT_STAGES) * FT_STAGE_BYTES + FT_TILE_BYTES;
 #pragma unroll
-                for (int k = 0; k < 4; k++)          // 64 keys = 4 steps of 16
-                    umma_bf16(t_o, umma_desc_sw128(pt + k * 32), umma_desc_mn_sw128(vt + k * 2048, 8192), idesc_o,
-                              (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(b_p_free);                            // P buffer free; O holds pages 0..j
+                for (int k = 0; k < 4; k++)          // 64 keys = 4 steps of 16; P: 8 columns of tensor memory a step
+                    umma_bf16_ts(t_o, t_s + (uint32_t)(j & 1) * 64 + k * 8, umma_desc_mn_sw128(vt + k * 2048, 8192),
+                                 idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                umma_commit(b_pv_done);                           // O holds pages 0..j
                 umma_commit(b_v_empty + (j % FT_STAGES) * 8);     // the stage's values have been read
             }
         }
@@ -246,7 +249,6 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(b_s_free + bsel * 8);
             // scale, mask, row maximum
             const int key0 = (pg_lo + j) * KB_PAGE;
             // four independent running maxima (one long dependent chain would leave the few resident warps idle)
@@ -277,13 +279,18 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                 m_ref = mx;
                 l *= f;
             }
-            // P V of page j - 1 is done: O holds pages 0..j-1 and the P buffer is free
-            if (j > 0) {
-                if (!(ok = mbar_wait(b_p_free, (uint32_t)(j - 1) & 1u, status))) break;
+            // P V of page j - 1 done means: O holds pages 0..j-1. Only a rescale of O has to wait for that here;
+            // otherwise the wait comes just before this page's P is handed over (it is taken once per page, in order,
+            // so that the barrier's phases cannot be mistaken for one another).
+            const bool rescale = __any_sync(0xffffffffu, grow) && j > 0;
+            bool waited_prev = j == 0;
+            if (!waited_prev && rescale) {
+                if (!(ok = mbar_wait(b_pv_done, (uint32_t)(j - 1) & 1u, status))) break;
                 __syncwarp();
                 tc_fence_after();
+                waited_prev = true;
             }
-            if (__any_sync(0xffffffffu, grow) && j > 0) {
+            if (rescale) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < 128; c0 += 32) {
                     uint32_t ov[32];
@@ -295,31 +302,35 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                 }
                 tmem_st_wait();
             }
-            // probabilities (relative to the reference), their sum, and P as bf16 into shared memory
+            // probabilities (relative to the reference), their sum, and P as bf16 into tensor memory
             const float mr = m_ref == -INFINITY ? 0.0f : m_ref;
-            uint8_t* prow = smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + r * 128;
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pv[32];                         // the row's 64 probabilities as bf16 pairs
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) {
-                uint32_t h[4];
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     const float p0 = ft_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * c]), scale_log2e, -mr));
                     const float p1 = ft_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * c + 1]), scale_log2e, -mr));
                     sum4[c] += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                    h[c] = *(uint32_t*)&v;
+                    pv[c8 * 4 + c] = *(uint32_t*)&v;
                 }
-                *(uint4*)(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // over the first 32 columns of this page's S buffer (the scores are in registers): the row's K index runs
+            // along the columns, two bf16 to a column, which is how the MMA reads an A operand from tensor memory
+            tmem_st_x32(t_s + lane_base + bsel * 64, pv);
+            tmem_st_wait();
+            if (!waited_prev) {
+                if (!(ok = mbar_wait(b_pv_done, (uint32_t)(j - 1) & 1u, status))) break;
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(b_p_ready);
         }
         // ---- O / l once the last P V is done
-        if (ok) ok = mbar_wait(b_p_free, (uint32_t)(n_iter - 1) & 1u, status);
+        if (ok) ok = mbar_wait(b_pv_done, (uint32_t)(n_iter - 1) & 1u, status);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after();
@@ -364,8 +375,8 @@ extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int*
     CUtensorMap map;
     int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
     if (rc) return rc;
-    // 112 KB of tiles + barriers + what aligning the base to 1024 can cost when it is aligned to 128: two CTAs fit
-    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + FT_P_BYTES + 256 + 768;
+    // 96 KB of tiles + barriers + what aligning the base to 1024 can cost when it is aligned to 128: two CTAs fit
+    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + 256 + 768;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(k_attn_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
