@@ -46,6 +46,30 @@ __device__ __forceinline__ float ft_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// two 32-bit floats in one 64-bit register and the packed arithmetic of sm_100 on them; a maximum of three
+__device__ __forceinline__ uint64_t ft_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void ft_unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ft_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t ft_add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float ft_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // shared-memory descriptor of an MN-major operand tile stored as rows of 128 bytes (64 elements of the MN dimension per
@@ -256,8 +280,10 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             if (key0 + 63 <= p_row && key0 >= lo_row) {
                 // the whole page lies inside this row's span (all pages but the last one or two): no masks
 #pragma unroll
-                for (int c = 0; c < 64; c++) {
-                    mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+                for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        mx4[k] = ft_max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
                 }
             } else {
 #pragma unroll
@@ -304,20 +330,32 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             }
             // probabilities (relative to the reference), their sum, and P as bf16 into tensor memory
             const float mr = m_ref == -INFINITY ? 0.0f : m_ref;
-            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // (two scores a time through the packed 32-bit multiply-add and add of sm_100: half as many instructions
+            // beside the exponentials, which is what a softmax warp's time goes to)
+            const uint64_t scale2 = ft_pack2(scale_log2e, scale_log2e), nmr2 = ft_pack2(-mr, -mr);
+            uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};         // four pairs of partial sums (bit pattern of 0.0f, 0.0f)
             uint32_t pv[32];                         // the row's 64 probabilities as bf16 pairs
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) {
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    const float p0 = ft_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * c]), scale_log2e, -mr));
-                    const float p1 = ft_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * c + 1]), scale_log2e, -mr));
-                    sum4[c] += p0 + p1;
+                    float x0, x1;
+                    ft_unpack2(ft_fma2(ft_pack2(__uint_as_float(sv[c8 * 8 + 2 * c]), __uint_as_float(sv[c8 * 8 + 2 * c + 1])),
+                                       scale2, nmr2), x0, x1);
+                    const float p0 = ft_exp2(x0), p1 = ft_exp2(x1);
+                    sum2[c] = ft_add2(sum2[c], ft_pack2(p0, p1));
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                     pv[c8 * 4 + c] = *(uint32_t*)&v;
                 }
             }
-            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            {
+                float a0, a1, b0, b1, c0, c1, d0, d1;
+                ft_unpack2(sum2[0], a0, a1);
+                ft_unpack2(sum2[1], b0, b1);
+                ft_unpack2(sum2[2], c0, c1);
+                ft_unpack2(sum2[3], d0, d1);
+                l += ((a0 + a1) + (b0 + b1)) + ((c0 + c1) + (d0 + d1));
+            }
             // over the first 32 columns of this page's S buffer (the scores are in registers): the row's K index runs
             // along the columns, two bf16 to a column, which is how the MMA reads an A operand from tensor memory
             tmem_st_x32(t_s + lane_base + bsel * 64, pv);
