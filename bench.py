@@ -30,6 +30,13 @@ sys.path.insert(0, ROOT)
 CONFIG_3B = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=166144, hidden_size=2560,
                  intermediate_size=10496, num_hidden_layers=32, num_attention_heads=20, num_key_value_heads=4,
                  head_dim=128, rms_norm_eps=1e-5, rope_theta=70000000.0, tie_word_embeddings=False)
+# the benchmark's two larger configurations (same architecture, other layer sizes), for runs with --preset
+CONFIG_16B = dict(CONFIG_3B, hidden_size=5120, intermediate_size=13824, num_hidden_layers=48, num_attention_heads=40,
+                  num_key_value_heads=8)
+CONFIG_33B = dict(CONFIG_3B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=40,
+                  num_key_value_heads=8)
+PRESETS = {"3b": ("Nanbeige4-3B-shaped llama-arch", CONFIG_3B), "16b": ("16B-class llama-arch", CONFIG_16B),
+           "33b": ("33B-class llama-arch", CONFIG_33B)}
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -94,13 +101,13 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_engine(layers: int, ctx: int, max_batch: int):
+def build_engine(layers: int, ctx: int, max_batch: int, base=None):
     import torch
     from kindi_b200.config import ModelConfig, architecture
     from kindi_b200.engine.engine import Engine
     from kindi_b200.parts.model import expected_tensors
     from kindi_b200.weights.random_init import random_tensors
-    cfg = dict(CONFIG_3B)
+    cfg = dict(base or CONFIG_3B)
     cfg["num_hidden_layers"] = layers
     mc = ModelConfig.from_dict(cfg)
     spec = architecture(mc.architecture).build_spec(mc)
@@ -138,6 +145,26 @@ def bench_prefill(eng, warmup: int, iters: int):
         eng.free(slot)
     eng.check_status()
     return statistics.median(times)
+
+
+def bench_unequal(eng, n_prompts: int = 8, new_tokens: int = 256):
+    """8 prompts of seeded random lengths 128..2048 that start together: one packed prompt step, then 256 greedy
+    tokens each, through Engine.generate_batch (host tokens in and out every step)"""
+    import random
+    import torch
+    rng = random.Random(11)
+    prompts = [[rng.randrange(eng.spec.vocab_size) for _ in range(rng.randint(128, 2048))] for _ in range(n_prompts)]
+    eng.generate_batch(prompts[:2], temperature=0.0, max_tokens=4)           # warm-up (graphs of other batch sizes aside)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = eng.generate_batch(prompts, temperature=0.0, max_tokens=new_tokens)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    made = sum(len(t) for t in res.tokens)
+    return {"prompts": n_prompts, "prompt_tokens": sum(len(p) for p in prompts), "new_tokens": made,
+            "seconds": round(dt, 4), "tokens_per_s": round(made / dt, 1),
+            "prompt_s": round(res.stats.prompt_s, 4), "decode_s": round(res.stats.gen_s, 4),
+            "decode_tokens_per_s": round(res.stats.gen_tok_s, 1), "steps": res.stats.steps}
 
 
 def fill_context(eng, batch: int, context: int):
@@ -210,7 +237,12 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--layers", type=int, default=CONFIG_3B["num_hidden_layers"])
+    ap.add_argument("--preset", default="3b", choices=sorted(PRESETS),
+                    help="layer sizes: the 3B-shaped configuration (default) or one of the two larger ones")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
+    ap.add_argument("--unequal", action="store_true",
+                    help="also generate for 8 prompts of random lengths 128 to 2048, 256 tokens each, through the "
+                         "Python entry point (the 16B-class configuration's workload)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the 2048-token prefill (for profiling)")
@@ -225,21 +257,25 @@ def main(argv=None) -> int:
         print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
         return 2
     a.warmup = max(3, a.warmup)
+    model_name, base = PRESETS[a.preset]
+    if a.layers <= 0:
+        a.layers = base["num_hidden_layers"]
     import torch
     from kindi_b200.engine.batch import layout
     pk = peaks()
     if a.no_pdl:
         from kindi_b200.kernels import lib as _K
         _K.set_pdl(False)
-    max_b = max(a.batch, 1 if a.no_points else 64)
+    point_batches = (1, 64) if a.preset == "3b" else (1,)          # 64 sequences of 8192 need too much cache beyond 3B
+    max_b = max(a.batch, 1 if a.no_points else max(point_batches))
     ctx = max_b * (a.context + a.steps * 2 + a.warmup + 256) + PREFILL_TOKENS + 64
     if a.prefill_only:
-        eng = build_engine(a.layers, PREFILL_TOKENS + 128, 2)
+        eng = build_engine(a.layers, PREFILL_TOKENS + 128, 2, base)
         pms = bench_prefill(eng, 2, max(1, min(a.steps, 3)))
         print(json.dumps({"prefill_only": True, "layers": a.layers, "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
                           "value": round(PREFILL_TOKENS * 1000.0 / pms, 1)}))
         return 0
-    eng = build_engine(a.layers, ctx, max_b)
+    eng = build_engine(a.layers, ctx, max_b, base)
     for g in eng.cache.groups:
         g.pool.normal_(0.0, 1.0)
     mc = eng.config
@@ -254,8 +290,8 @@ def main(argv=None) -> int:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02) seed 0, synthetic token ids, cache filled with N(0,1)",
         "impl": "ours",
-        "config": {"model": "Nanbeige4-3B-shaped llama-arch", "global_batch": a.batch, "seq_len": a.context,
-                   "parallelism": "none (1 GPU)", "layers": a.layers, "layers_of_config": CONFIG_3B["num_hidden_layers"],
+        "config": {"model": model_name, "global_batch": a.batch, "seq_len": a.context,
+                   "parallelism": "none (1 GPU)", "layers": a.layers, "layers_of_config": base["num_hidden_layers"],
                    "hidden_size": mc.hidden_size, "heads": mc.num_attention_heads, "kv_heads": mc.num_key_value_heads,
                    "head_dim": mc.head_dim, "intermediate_size": mc.intermediate_size, "vocab_size": mc.vocab_size,
                    "rope_theta": mc.rope_theta, "rms_norm_eps": mc.rms_norm_eps, "tied": mc.tie_word_embeddings,
@@ -278,10 +314,12 @@ def main(argv=None) -> int:
                           "frac": round(fl / (pms / 1000.0) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"],
                           "tflop": round(fl / 1e12, 3)}
         pts = {}
-        for b in (1, 64):
+        for b in point_batches:
             ms, _, _, _ = bench_decode(eng, b, a.context, max(16, a.steps // 2), a.warmup, False)
             pts["decode_b%d" % b] = round(b * 1000.0 / ms, 1)
         out["points"] = pts
+    if a.unequal:
+        out["unequal_batch"] = bench_unequal(eng)
     print(json.dumps(out))
     return 0
 
