@@ -180,30 +180,29 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
             const int p0 = (tp * MT + mt) * TC_BM;
             const int prow = p0 + quarter * 32 + lane;           // row of the 128-row side this thread holds
             const uint32_t tbase = tmem + (acc + mt) * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-            if (!SWAP && BN % 128 == 0 && swiglu_ld > 0) {
-                // the weights' rows come in groups of 64 gate rows followed by the 64 up rows of the same outputs, so
-                // a tile holds both halves of BN / 2 outputs: out[token][j] = silu(gate) * up goes out as bf16 and the
-                // 2F-wide product is never written
+            if (!SWAP && BN % 32 == 0 && swiglu_ld > 0) {
+                // the weights' rows come in groups of 16 gate rows followed by the 16 up rows of the same outputs, so
+                // every 32 columns of a tile hold both halves of 16 outputs: out[token][j] = silu(gate) * up goes out
+                // as bf16 and the 2F-wide product is never written
                 // (every lane of the warp takes part in the warp-wide TMEM loads; only the stores depend on the row)
                 bf16* orow = (bf16*)C + (size_t)prow * swiglu_ld;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if ((c0 & 64) || q0 + c0 >= rowsQ) continue;                   // up columns; past the end
-                    uint32_t g[16], u[16];
-                    tmem_ld_32x16(tbase + c0, g);
-                    tmem_ld_32x16(tbase + c0 + 64, u);
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (q0 + c0 >= rowsQ) continue;                   // past the end (uniform over the warp)
+                    uint32_t gu[32];
+                    tmem_ld_32x32(tbase + c0, gu);
                     tmem_ld_wait();
                     if (prow < rowsP) {
                         uint32_t h[8];
 #pragma unroll
                         for (int c = 0; c < 8; c++) {
-                            const float g0 = __uint_as_float(g[2 * c]), g1 = __uint_as_float(g[2 * c + 1]);
+                            const float g0 = __uint_as_float(gu[2 * c]), g1 = __uint_as_float(gu[2 * c + 1]);
                             __nv_bfloat162 v = __floats2bfloat162_rn(
-                                __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(u[2 * c]),
-                                __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(u[2 * c + 1]));
+                                __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(gu[16 + 2 * c]),
+                                __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(gu[16 + 2 * c + 1]));
                             h[c] = *(uint32_t*)&v;
                         }
-                        bf16* dst = orow + ((q0 + c0) >> 7) * 64 + (c0 & 63);
+                        bf16* dst = orow + ((q0 + c0) >> 1);
                         *(uint4*)(dst) = make_uint4(h[0], h[1], h[2], h[3]);
                         *(uint4*)(dst + 8) = make_uint4(h[4], h[5], h[6], h[7]);
                     }
@@ -323,7 +322,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
     int z = (total_kb + kbps - 1) / kbps;               // every split has at least one k-block
     const int units = ((rowsP + MT * TC_BM - 1) / (MT * TC_BM)) * ((rowsQ + BN - 1) / BN) * z;
     const int grid = units < kb_sm_count() ? units : kb_sm_count();
-    if (swiglu_ld > 0 && (SWAP || BN % 128 || sizeof(TC) != 2 || z != 1)) return (int)cudaErrorInvalidValue;
+    if (swiglu_ld > 0 && (SWAP || BN % 32 || sizeof(TC) != 2 || z != 1)) return (int)cudaErrorInvalidValue;
     kb_launch(kern, grid, TC_THREADS, S::TOTAL, st, mp, mq, (TC*)C, rowsP, rowsQ, K, ldc, split_stride, kbps, z, status,
               swiglu_ld);
     return (int)cudaGetLastError();
@@ -340,13 +339,13 @@ extern "C" int kb_gemm_tc_splits(int K, int wanted) {
 
 // C[M][N] (+ split planes) = A[M][K] W[N][K]^T. cdtype: KB_F32 or KB_BF16 (bf16 only without splits).
 // swap = 0: prefill form (tile 128 tokens x bn features); swap = 1: decode form (tile 128 features x bn tokens).
-// swiglu != 0 (prefill form, bn 128 or 256, bf16 out): W holds gate and up rows in groups of 64 + 64 and C is the
-// bf16 [M][N / 2] result silu(gate) * up with row stride ldc.
+// swiglu != 0 (prefill form, bn a multiple of 32, bf16 out): W holds gate and up rows in groups of 16 + 16 and C is
+// the bf16 [M][N / 2] result silu(gate) * up with row stride ldc.
 extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int M, int N, int K, int lda, int ldw,
                           int ldc, int swap, int bn, int splits, long long split_stride, int* status,
                           cudaStream_t st, int swiglu = 0, int mt = 1) {
     if (mt != 1 && (mt != 2 || swap || splits != 1)) return (int)cudaErrorInvalidValue;
-    if (swiglu && (swap || (N % 128) || cdtype != KB_BF16 || splits != 1 || (ldc % 8) || ((uintptr_t)C & 15)))
+    if (swiglu && (swap || (N % 32) || cdtype != KB_BF16 || splits != 1 || (ldc % 8) || ((uintptr_t)C & 15)))
         return (int)cudaErrorInvalidValue;
     const int swiglu_ld = swiglu ? ldc : 0;
     if (M <= 0 || N <= 0 || K <= 0) return 0;

@@ -67,7 +67,7 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
     best, best_cost = (128, 1), None
     for mt in ((1, 2) if m >= 256 else (1,)):
         for bn in (256, 240, 224, 208, 192, 176, 160, 144, 128):
-            if swiglu and bn not in (128, 256):
+            if swiglu and bn % 32:
                 continue
             units = -(-m // (128 * mt)) * -(-n // bn)
             t_kb = max(0.276 * mt * bn / 256.0, 1.15e-3 * (128 * mt + bn))
@@ -110,9 +110,9 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
 
 def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
     """out (bf16 [M, F]) = silu(g) * u for a prompt-sized step, finished inside the product's epilogue; w_grouped
-    [2F, K] holds 64 gate rows then the 64 up rows of the same outputs, group after group. False: not taken"""
+    [2F, K] holds 16 gate rows then the 16 up rows of the same outputs, group after group. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
-    if m <= SMALL_M or not _tc_ok(a, w_grouped) or n % 128 or not out.is_contiguous() or (n // 2) % 8:
+    if m <= SMALL_M or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
         return False
     bn, mt = _prefill_tile(m, n, a.shape[1], swiglu=True)
     K.gemm_tc(a, w_grouped, out, swap=False, bn=bn, splits=1, status=status, swiglu=True, mt=mt)

@@ -230,8 +230,8 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,
             status: torch.Tensor, swiglu: bool = False, mt: int = 1) -> None:
     """out = a[M, K] @ w[N, K]^T on the tensor cores (bf16 in, fp32 accumulate). ``out`` is [M, N] (bf16 or fp32)
-    or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits). ``swiglu`` (prefill form, bn 128 or 256):
-    w holds 64 gate rows then the 64 up rows of the same outputs, group after group, and ``out`` is the bf16
+    or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits). ``swiglu`` (prefill form, bn a multiple
+    of 32): w holds 16 gate rows then the 16 up rows of the same outputs, group after group, and ``out`` is the bf16
     [M, N / 2] result silu(gate) * up. ``mt`` = 2 (prefill form): a unit is two 128-row tiles over the same columns"""
     _need_cuda(a, w, out)
     M, K = a.shape
@@ -239,7 +239,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, 
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert a.stride(1) == 1 and w.stride(1) == 1 and out.is_contiguous()
     if swiglu:
-        assert out.shape == (M, N // 2) and out.dtype == torch.bfloat16 and not swap and splits == 1 and N % 128 == 0
+        assert out.shape == (M, N // 2) and out.dtype == torch.bfloat16 and not swap and splits == 1 and N % 32 == 0 and bn % 32 == 0
         stride, ldc = 0, N // 2
     elif out.dim() == 3:
         assert out.shape == (gemm_tc_splits(K, splits), M, N) and out.dtype == torch.float32

@@ -29,11 +29,12 @@ class SwiGLU(FeedForward):
         g, u = weights("gate_proj.weight"), weights("up_proj.weight")
         if g.dtype != u.dtype:
             raise ValueError("gate and up weights of %s are stored in different dtypes" % weights.prefix)
-        # gate and up rows in groups of 64: 64 gate rows, then the 64 up rows of the same outputs. A tile of the
-        # product then holds both halves of its outputs, so a prompt-sized product finishes SwiGLU in its epilogue;
-        # the stand-alone SwiGLU kernel reads the same grouping. (Sizes that are no multiple of 64: all gates, then
-        # all ups.)
-        self.group = 64 if self.f % 64 == 0 else self.f
+        # gate and up rows in groups of 16: 16 gate rows, then the 16 up rows of the same outputs. A tile of the
+        # product then holds both halves of its outputs (32 neighbouring accumulator columns of a prompt-sized product,
+        # the two half-warps of 32 accumulator lanes of a decode-sized one), so SwiGLU is finished in the product's
+        # epilogue; the stand-alone SwiGLU kernel reads the same grouping. (Sizes that are no multiple of 16: all
+        # gates, then all ups.)
+        self.group = 16 if self.f % 16 == 0 else self.f
         n = self.f // self.group
         self.wgu = torch.stack([g.view(n, self.group, width), u.view(n, self.group, width)], dim=1) \
             .reshape(2 * self.f, width).contiguous()
@@ -42,7 +43,7 @@ class SwiGLU(FeedForward):
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:
         from ..kernels import fast
         h = torch.empty((y.shape[0], self.f), dtype=self.dtype, device=y.device)
-        if not (ctx.fast and self.group == 64 and fast.gemm_swiglu_rows(y, self.wgu, h, ctx.status)):
+        if not (ctx.fast and self.group == 16 and fast.gemm_swiglu_rows(y, self.wgu, h, ctx.status)):
             gu = L.rows_or_planes(ctx, y, self.wgu, self.dtype)
             K.swiglu(gu, h, self.group)
         return Branch(L.planes(ctx, h, self.wd))

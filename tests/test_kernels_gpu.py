@@ -234,13 +234,14 @@ def test_attention_decode_rotates_and_stores_by_itself(K, nh, nkv, hd, window, p
     assert _rel(got2.float(), want.float()) < 1e-2          # other splits: another order of the merge
 
 
-@pytest.mark.parametrize("M,F,K_,bn", [(129, 64, 128, 128), (2048, 1024, 520, 256), (300, 320, 264, 256), (200, 192, 72, 128)])
+@pytest.mark.parametrize("M,F,K_,bn", [(129, 64, 128, 128), (2048, 1024, 520, 256), (300, 320, 264, 256), (200, 192, 72, 128),
+                                       (260, 176, 136, 160), (150, 48, 64, 224)])
 def test_gemm_tc_finishes_swiglu_in_its_epilogue(K, M, F, K_, bn):
     g = torch.Generator(device="cuda").manual_seed(M + F + K_)
     a = (torch.randn(M, K_, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
     wg = (torch.randn(F, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
     wu = (torch.randn(F, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
-    wgu = torch.stack([wg.view(F // 64, 64, K_), wu.view(F // 64, 64, K_)], dim=1).reshape(2 * F, K_).contiguous()
+    wgu = torch.stack([wg.view(F // 16, 16, K_), wu.view(F // 16, 16, K_)], dim=1).reshape(2 * F, K_).contiguous()
     st = _status()
     out = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
     K.gemm_tc(a, wgu, out, swap=False, bn=bn, splits=1, status=st, swiglu=True)
@@ -252,10 +253,10 @@ def test_gemm_tc_finishes_swiglu_in_its_epilogue(K, M, F, K_, bn):
     rows = torch.empty(M, 2 * F, device="cuda", dtype=torch.bfloat16)
     K.gemm_tc(a, wgu, rows, swap=False, bn=bn, splits=1, status=st)
     h = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
-    K.swiglu(rows, h, 64)
+    K.swiglu(rows, h, 16)
     assert _rel(h.float(), ref) < 1.5e-2
     planes = rows.float()[None].contiguous()
-    K.swiglu(planes, h, 64)
+    K.swiglu(planes, h, 16)
     assert _rel(h.float(), ref) < 1.5e-2
 
 
@@ -288,10 +289,10 @@ def test_gemm_tc_two_row_tiles(K, M, N, K_, bn):
         K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=st, mt=2)
         assert int(st.item()) == 0
         assert _rel(out.float(), ref) < tol
-    if bn in (128, 256) and N % 128 == 0:
+    if bn % 32 == 0 and N % 32 == 0:
         F = N // 2
         wg, wu = w[:F], w[F:]
-        wgu = torch.stack([wg.view(F // 64, 64, K_), wu.view(F // 64, 64, K_)], dim=1).reshape(N, K_).contiguous()
+        wgu = torch.stack([wg.view(F // 16, 16, K_), wu.view(F // 16, 16, K_)], dim=1).reshape(N, K_).contiguous()
         h = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
         K.gemm_tc(a * 0.1, wgu, h, swap=False, bn=bn, splits=1, status=st, swiglu=True, mt=2)
         gg, uu = (a * 0.1).double() @ wg.double().T, (a * 0.1).double() @ wu.double().T
@@ -326,7 +327,7 @@ def test_add_rmsnorm(K, T, E, planes, ydtype):
 
 
 @pytest.mark.parametrize("T,F,group,planes", [(3, 50, 0, 0), (9, 193, 0, 3), (8, 10496, 64, 5), (700, 320, 64, 0),
-                                              (130, 64, 64, 1)])
+                                              (130, 64, 64, 1), (8, 10496, 16, 8), (600, 176, 16, 0), (5, 48, 16, 2)])
 def test_swiglu(K, T, F, group, planes):
     g = torch.Generator(device="cuda").manual_seed(T + F)
     gate = torch.randn(T, F, device="cuda", generator=g) * 2
