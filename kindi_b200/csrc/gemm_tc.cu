@@ -328,6 +328,245 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
     return (int)cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Gate/up product of a decode step with SwiGLU finished inside the product: H[M][F] = silu(g) * u, bf16.
+//
+// The decode form again (weights on the 128-row side, 16 gate rows then the 16 up rows of the same outputs, so a
+// quarter of a tile's rows = one epilogue warp's lanes holds both halves of 16 outputs), but the work is cut
+// differently: all (tile, K block) pairs are laid out in one line, tile after tile, and CTA c takes the c-th stretch of
+// it. A stretch is at least one tile long, so a tile is shared by at most two CTAs: the one that holds its first K
+// blocks at the END of its stretch (its owner) and the next CTA, which holds the rest at the START of its own
+// stretch. The second writes its 32-bit partial tile and raises the tile's flag as the first thing it does; the owner
+// meets the flag long set when it comes to the tile, adds the partial in a fixed order (own + other), applies
+// SwiGLU and lowers the flag. No split-K planes are written or read again, no SwiGLU kernel follows, and every CTA
+// streams the same number of K blocks. The owner's wait is bounded like every wait here.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS) k_gemm_sk_swiglu(const __grid_constant__ CUtensorMap mapP,
+        const __grid_constant__ CUtensorMap mapQ, bf16* __restrict__ H, int rowsP, int M, int K, int F, int ldh,
+        float* __restrict__ part, int* __restrict__ flags, int* status) {
+    using S = TcSmem<BN, STAGES, 1, true>;
+    extern __shared__ uint8_t smem_raw[];
+    kb_pdl_launch_now();
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + S::BAR_OFF, bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_acc_full = bar_empty + STAGES * 8, bar_acc_empty = bar_acc_full + 16;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + S::BAR_OFF + S::N_BARS * 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tilesP = (rowsP + TC_BM - 1) / TC_BM;
+    const int KB = (K + TC_BK - 1) / TC_BK;
+    const int total = tilesP * KB;                                       // (the launcher refuses sizes beyond an int)
+    const int W = (total + (int)gridDim.x - 1) / (int)gridDim.x;         // >= KB because gridDim.x <= tilesP
+    const int L0 = min(total, (int)blockIdx.x * W), L1 = min(total, L0 + W);
+    constexpr uint32_t TMEM_COLS = BN <= 16 ? 32 : BN <= 32 ? 64 : BN <= 64 ? 128 : 256;
+    constexpr uint32_t ACC_COLS = TMEM_COLS / 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_acc_full + a * 8, 1);
+            mbar_init(bar_acc_empty + a * 8, 4);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&mapP);
+        tma_prefetch_desc(&mapQ);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0 && L0 < L1) {
+            // the first stage's weights are requested before the wait on the preceding kernel (see k_gemm_tc)
+            bool ok = true;
+            int tile = L0 / KB, kb = L0 % KB;
+            mbar_expect_tx(bar_full, S::STAGE_BYTES);
+            tma_load_2d(sbase, &mapP, kb * TC_BK, tile * TC_BM, bar_full);
+            kb_pdl_wait();
+            tma_load_2d(sbase + S::A_BYTES, &mapQ, kb * TC_BK, 0, bar_full);
+            uint32_t n = 1;
+            for (int L = L0 + 1; L < L1 && ok; L++, n++) {
+                if (++kb == KB) {
+                    kb = 0;
+                    tile++;
+                }
+                const int s = n % STAGES;
+                if (!(ok = mbar_wait(bar_empty + s * 8, ((n / STAGES) & 1u) ^ 1u, status))) break;
+                mbar_expect_tx(bar_full + s * 8, S::STAGE_BYTES);
+                const uint32_t dst = sbase + s * S::STAGE_BYTES;
+                tma_load_2d(dst, &mapP, kb * TC_BK, tile * TC_BM, bar_full + s * 8);
+                tma_load_2d(dst + S::A_BYTES, &mapQ, kb * TC_BK, 0, bar_full + s * 8);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+            uint32_t n = 0, seg = 0;
+            bool ok = true;
+            int kb = L0 % KB - 1;
+            for (int L = L0; L < L1 && ok; L++, n++) {
+                if (++kb == KB) kb = 0;
+                const bool first = L == L0 || kb == 0, last = L == L1 - 1 || kb == KB - 1;
+                const uint32_t acc = seg & 1u;
+                if (first) {
+                    if (!(ok = mbar_wait(bar_acc_empty + acc * 8, ((seg >> 1) & 1u) ^ 1u, status))) break;
+                    tc_fence_after();
+                }
+                const int s = n % STAGES;
+                if (!(ok = mbar_wait(bar_full + s * 8, (n / STAGES) & 1u, status))) break;
+                tc_fence_after();
+                const uint32_t a = sbase + s * S::STAGE_BYTES, b = a + S::A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++)
+                    umma_bf16(tmem + acc * ACC_COLS, umma_desc_sw128(a + k * 32), umma_desc_sw128(b + k * 32), idesc,
+                              (!first || k > 0) ? 1u : 0u);
+                umma_commit(bar_empty + s * 8);
+                if (last) {
+                    umma_commit(bar_acc_full + acc * 8);
+                    seg++;
+                }
+            }
+        }
+    } else {
+        // epilogue warps 2..5 own TMEM lanes 32 * (warp % 4) .. + 31 = one group of 16 gate + 16 up rows of a tile
+        const int quarter = warp & 3;
+        const bool leader = threadIdx.x == 64;                       // one thread of the four warps talks to the flags
+        uint32_t seg = 0;
+        bool ok = true;
+        kb_pdl_wait();
+        for (int L = L0; L < L1 && ok; seg++) {
+            const int tile = L / KB, kb0 = L % KB;
+            const int Lend = min(L1, L + (KB - kb0));          // one past the stretch's last K block of this tile
+            const bool helper = kb0 > 0;                             // the tile's first K blocks belong to the CTA before
+            const bool shared_owner = !helper && Lend - L < KB;
+            L = Lend;
+            const uint32_t acc = seg & 1u;
+            float* ptile = part + (size_t)tile * BN * TC_BM + quarter * 32 + lane;     // + token * 128
+            float other[BN];                      // the other CTA's partial sums of this thread's row (shared tiles)
+            if (shared_owner) {
+                // The other part was written when the next CTA began, long ago: fetch it now, while this CTA's own K
+                // blocks of the tile are still being multiplied, and lower the flag for the next call.
+                if (leader) {
+                    const uint64_t t0 = kb_globaltimer();
+                    while (*((volatile int*)(flags + tile)) == 0) {
+                        if (kb_globaltimer() - t0 > KB_WAIT_NS) {
+                            atomicOr(status, KB_ST_WAIT_TIMEOUT);
+                            break;
+                        }
+                    }
+                    __threadfence();
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < BN; c++) other[c] = c < M ? __ldcg(ptile + (size_t)c * TC_BM) : 0.0f;
+                // (every thread's loads above have returned before it passes this barrier: their values are used below
+                // only after it, and the compiler keeps the loads before the barrier's memory clobber)
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (leader) atomicExch(flags + tile, 0);
+            }
+            ok = mbar_wait(bar_acc_full + acc * 8, (seg >> 1) & 1u, status);
+            {
+                // the four warps go on together or not at all (they meet at barriers, which have no time limit)
+                uint32_t any_bad;
+                asm volatile(
+                    "{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n bar.red.or.pred q, 2, 128, p;\n selp.u32 %0, 1, 0, q;\n}"
+                    : "=r"(any_bad)
+                    : "r"(ok ? 0u : 1u)
+                    : "memory");
+                if (any_bad) {
+                    ok = false;
+                    break;
+                }
+            }
+            tc_fence_after();
+            const uint32_t tbase = tmem + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            const int feat = tile * 64 + quarter * 16 + (lane & 15);
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld_32x16(tbase + c0, r);
+                tmem_ld_wait();
+                if (helper) {
+#pragma unroll
+                    for (int c = 0; c < 16; c++)
+                        if (c0 + c < M) ptile[(size_t)(c0 + c) * TC_BM] = __uint_as_float(r[c]);
+                    continue;
+                }
+#pragma unroll
+                for (int c = 0; c < 16; c++) {
+                    float v = __uint_as_float(r[c]);
+                    if (shared_owner) v += other[c0 + c];
+                    const float u = __shfl_xor_sync(0xffffffffu, v, 16);          // lanes 0..15: gate; their partners: up
+                    if (lane < 16 && c0 + c < M && feat < F)
+                        H[(size_t)(c0 + c) * ldh + feat] = __float2bfloat16_rn(__fdividef(v, 1.0f + __expf(-v)) * u);
+                }
+            }
+            if (helper) {
+                __threadfence();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (leader) atomicExch(flags + tile, 1);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + acc * 8);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+template <int BN, int STAGES>
+static int launch_sk_swiglu(const CUtensorMap& mp, const CUtensorMap& mq, void* H, int rowsP, int M, int K, int F,
+                            int ldh, float* part, int* flags, int* status, cudaStream_t st) {
+    using S = TcSmem<BN, STAGES, 1, true>;
+    auto kern = k_gemm_sk_swiglu<BN, STAGES>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const int tilesP = (rowsP + TC_BM - 1) / TC_BM;
+    const int grid = tilesP < kb_sm_count() ? tilesP : kb_sm_count();
+    kb_launch(kern, grid, TC_THREADS, S::TOTAL, st, mp, mq, (bf16*)H, rowsP, M, K, F, ldh, part, flags, status);
+    return (int)cudaGetLastError();
+}
+
+// H[M][F] (bf16, row stride ldh) = silu(g) * u with [g | u] = A[M][K] W[2F][K]^T, W in groups of 16 gate rows and the 16
+// up rows of the same outputs; M <= bn in {16, 32, 64, 128}. `part` ([ceil(2F / 128)][bn][128] floats) and `flags`
+// ([ceil(2F / 128)] ints, zero before the first call and left zero by every call that ends without an error) are the
+// caller's; calls that share them must be ordered on one stream.
+extern "C" int kb_gemm_swiglu_decode(const void* A, const void* W, void* H, int M, int F, int K, int lda, int ldw, int ldh,
+                                     int bn, float* part, int* flags, int* status, cudaStream_t st) {
+    if (M <= 0 || F <= 0 || K <= 0) return 0;
+    if ((K % 8) || (lda % 8) || (ldw % 8) || (F % 16) || M > bn || !part || !flags) return (int)cudaErrorInvalidValue;
+    if ((long long)((2 * (long long)F + TC_BM - 1) / TC_BM) * ((K + TC_BK - 1) / TC_BK) > 0x3fffffffLL)
+        return (int)cudaErrorInvalidValue;
+    CUtensorMap mp, mq;
+    int rc;
+    if ((rc = kb_make_map_bf16(&mp, W, 2 * F, K, ldw, TC_BM))) return rc;
+    if ((rc = kb_make_map_bf16(&mq, A, M, K, lda, bn))) return rc;
+    switch (bn) {
+        case 16: return launch_sk_swiglu<16, 8>(mp, mq, H, 2 * F, M, K, F, ldh, part, flags, status, st);
+        case 32: return launch_sk_swiglu<32, 8>(mp, mq, H, 2 * F, M, K, F, ldh, part, flags, status, st);
+        case 64: return launch_sk_swiglu<64, 8>(mp, mq, H, 2 * F, M, K, F, ldh, part, flags, status, st);
+        case 128: return launch_sk_swiglu<128, 5>(mp, mq, H, 2 * F, M, K, F, ldh, part, flags, status, st);
+        default: return (int)cudaErrorInvalidValue;
+    }
+}
+
 // how many K splits the launch will use for a wanted number (the caller sizes the partial planes with it)
 extern "C" int kb_gemm_tc_splits(int K, int wanted) {
     const int total_kb = (K + TC_BK - 1) / TC_BK;

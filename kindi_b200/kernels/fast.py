@@ -119,6 +119,26 @@ def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor
     return True
 
 
+_SK_SCRATCH = {}           # (device, tiles, bn) -> (partial tiles, flags): scratch of the decode gate/up product
+
+
+def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
+    """out (bf16 [M, F]) = silu(g) * u for a decode-sized step, finished inside the product (no split-K planes, no
+    SwiGLU kernel); w_grouped [2F, K] as for gemm_swiglu_rows. False: not taken"""
+    m, n = a.shape[0], w_grouped.shape[0]
+    if m > 32 or not _tc_ok(a, w_grouped) or n % 32 or out.stride(1) != 1 or out.dtype != torch.bfloat16:
+        return False        # (from 33 rows on it is level with the split-K product followed by the SwiGLU kernel)
+    bn = _swap_bn(m)
+    tiles = -(-n // 128)
+    key = (a.device, tiles, bn)
+    if key not in _SK_SCRATCH:
+        _SK_SCRATCH[key] = (torch.empty(tiles * bn * 128, dtype=torch.float32, device=a.device),
+                            torch.zeros(tiles, dtype=torch.int32, device=a.device))
+    part, flags = _SK_SCRATCH[key]
+    K.gemm_swiglu_decode(a, w_grouped, out, bn, part, flags, status)
+    return True
+
+
 def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages) -> bool:
     """the tensor-core attention kernel, where it takes the shape: head size 64 or 128, bf16, aligned rows"""
     if hd not in (64, 128) or q.dtype != torch.bfloat16 or q.stride(0) % 8 or q.data_ptr() % 16:

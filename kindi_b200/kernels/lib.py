@@ -42,6 +42,8 @@ _SIGS = {
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_longlong, c_void_p, c_void_p, c_int, c_int],
     "kb_gemm_tc_splits": [c_int, c_int],
+    "kb_gemm_swiglu_decode": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                              c_void_p, c_void_p, c_void_p],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_attn_decode_rope": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -249,6 +251,25 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, 
         stride, ldc = 0, N
     _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, 1 if swap else 0,
                              bn, splits, stride, _p(status), _stream(), 1 if swiglu else 0, mt), "gemm_tc")
+
+
+def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, bn: int, part: torch.Tensor,
+                       flags: torch.Tensor, status: torch.Tensor) -> None:
+    """out (bf16 [M, F]) = silu(g) * u with [g | u] = a[M, K] @ w_grouped[2F, K]^T (16 gate rows, then the 16 up rows
+    of the same outputs), for M <= bn rows, SwiGLU finished inside the product. ``part`` (float32, at least
+    ceil(2F / 128) * bn * 128) and ``flags`` (int32 zeros, at least ceil(2F / 128)) are scratch that calls on one
+    stream may share"""
+    _need_cuda(a, w_grouped, out, part, flags)
+    M, K = a.shape
+    F = w_grouped.shape[0] // 2
+    tiles = -(-2 * F // 128)
+    assert a.dtype == w_grouped.dtype == out.dtype == torch.bfloat16 and w_grouped.shape == (2 * F, K)
+    assert a.stride(1) == 1 and w_grouped.stride(1) == 1 and out.shape == (M, F) and out.stride(1) == 1
+    assert F % 16 == 0 and M <= bn and part.dtype == torch.float32 and part.numel() >= tiles * bn * 128
+    assert flags.dtype == torch.int32 and flags.numel() >= tiles
+    _check(load().kb_gemm_swiglu_decode(_p(a), _p(w_grouped), _p(out), M, F, K, a.stride(0), w_grouped.stride(0),
+                                        out.stride(0), bn, _p(part), _p(flags), _p(status), _stream()),
+           "gemm_swiglu_decode")
 
 
 def gemm_tc_splits(K: int, wanted: int) -> int:

@@ -43,7 +43,9 @@ class SwiGLU(FeedForward):
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:
         from ..kernels import fast
         h = torch.empty((y.shape[0], self.f), dtype=self.dtype, device=y.device)
-        if not (ctx.fast and self.group == 16 and fast.gemm_swiglu_rows(y, self.wgu, h, ctx.status)):
+        fused = ctx.fast and self.group == 16 and (fast.gemm_swiglu_decode(y, self.wgu, h, ctx.status)
+                                                   or fast.gemm_swiglu_rows(y, self.wgu, h, ctx.status))
+        if not fused:
             gu = L.rows_or_planes(ctx, y, self.wgu, self.dtype)
             K.swiglu(gu, h, self.group)
         return Branch(L.planes(ctx, h, self.wd))

@@ -299,6 +299,37 @@ def test_gemm_tc_two_row_tiles(K, M, N, K_, bn):
         assert _rel(h.float(), gg / (1 + torch.exp(-gg)) * uu) < 6e-3
 
 
+@pytest.mark.parametrize("M,F,K_", [(8, 10496, 2560), (1, 48, 64), (16, 64, 72), (17, 1008, 264), (64, 2656, 328),
+                                    (100, 512, 1096), (5, 9488, 200), (3, 9472, 136)])
+def test_decode_gate_up_product_finishes_swiglu_itself(K, M, F, K_):
+    """the decode-sized gate/up product whose CTAs take equal stretches of all (tile, K block) pairs and meet in shared
+    tiles: against the plain formula, twice in a row over the same scratch (flags are left as they were found), and
+    with as many tiles as there are CTAs, fewer, and more"""
+    from kindi_b200.kernels import fast
+    g = torch.Generator(device="cuda").manual_seed(M + F + K_)
+    a = (torch.randn(M, K_, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    wg = (torch.randn(F, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(F, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    wgu = torch.stack([wg.view(F // 16, 16, K_), wu.view(F // 16, 16, K_)], dim=1).reshape(2 * F, K_).contiguous()
+    gg, uu = a.double() @ wg.double().T, a.double() @ wu.double().T
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    st = _status()
+    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = -(-2 * F // 128)
+    part = torch.full((tiles * bn * 128,), float("nan"), device="cuda")
+    flags = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        out = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+        K.gemm_swiglu_decode(a, wgu, out, bn, part, flags, st)
+        assert int(st.item()) == 0
+        assert _rel(out.float(), ref) < 6e-3
+        assert int(flags.abs().sum().item()) == 0
+    if M <= 32:
+        out = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+        assert fast.gemm_swiglu_decode(a, wgu, out, st)          # the engine's way in, with scratch of its own
+        assert int(st.item()) == 0 and _rel(out.float(), ref) < 6e-3
+
+
 # ------------------------------------------------------------------------------------------------ small kernels
 @pytest.mark.parametrize("T,E,planes", [(3, 50, 0), (8, 2560, 7), (5, 72, 3), (600, 2560, 1), (600, 96, 9), (70, 4100, 2),
                                         (520, 1000, 2), (513, 2048, 0), (600, 3200, 1)])
