@@ -229,6 +229,8 @@ class Engine:
     def _raise_status(self, st: int) -> None:
         if st:
             self.status.zero_()
+            from ..kernels import fast
+            fast.reset_scratch()
             what = [n for bit, n in ((K.ST_BAD_TOKEN, "a token id outside the vocabulary"),
                                      (K.ST_BAD_PAGE, "a cache position without a mapped page"),
                                      (K.ST_WAIT_TIMEOUT, "a wait inside a kernel ran out"),

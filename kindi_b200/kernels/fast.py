@@ -122,6 +122,13 @@ def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor
 _SK_SCRATCH = {}           # (device, tiles, bn) -> (partial tiles, flags): scratch of the decode gate/up product
 
 
+def reset_scratch() -> None:
+    """lower every flag of the decode gate/up product's scratch: after a step whose kernels reported an error (a wait
+    that ran out can leave a flag raised, which the next step would take for a partial tile that is there)"""
+    for _, flags in _SK_SCRATCH.values():
+        flags.zero_()
+
+
 def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
     """out (bf16 [M, F]) = silu(g) * u for a decode-sized step, finished inside the product (no split-K planes, no
     SwiGLU kernel); w_grouped [2F, K] as for gemm_swiglu_rows. False: not taken"""
