@@ -18,15 +18,13 @@
 // memory is only rescaled, by tcgen05.ld / tcgen05.st) when a row's maximum has grown by more than 8 (a factor 256 in
 // the probabilities, which bf16 and the 32-bit sums hold without loss); the final division by the row sum makes the
 // result the same as with an exact running maximum (kindi/nbq_fa.cu:31-151 is the recurrence this follows).
-// Head size 128. Every wait is bounded (sm100.cuh); all tcgen05 loads and stores are executed by whole warps.
+// Head sizes 64 and 128. Every wait is bounded (sm100.cuh); all tcgen05 loads and stores are executed by whole warps.
 #include "sm100.cuh"
 
 #define FT_THREADS 192
 #define FT_STAGES 2
-#define FT_HD 128
-#define FT_TILE_BYTES (64 * FT_HD * 2)           // one page of keys (or values) of one head: 16 KB
-#define FT_STAGE_BYTES (2 * FT_TILE_BYTES)
-#define FT_Q_BYTES (128 * FT_HD * 2)             // 32 KB: two K-blocks of [128 rows][64 columns]
+// per head size HD (64 or 128): a page of keys (or values) of one head is 64 * HD * 2 bytes, a stage holds one of
+// each, Q is HD / 64 blocks of [128 rows][64 columns]
 #define FT_LAZY 8.0f
 
 __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) { tmem_ld_32x32(taddr, r); }
@@ -85,10 +83,12 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
     return d;
 }
 
+template <int FT_HD>
 __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
         const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
         const int* __restrict__ table, int table_stride, int n_pages, int* status) {
+    constexpr int FT_TILE_BYTES = 64 * FT_HD * 2, FT_STAGE_BYTES = 2 * FT_TILE_BYTES, FT_Q_BYTES = 128 * FT_HD * 2;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -139,8 +139,8 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
 
     // ---- Q into shared memory: two K-blocks of [128 rows][64 columns], rows of 128 bytes, 128-byte swizzle
     if (active) {
-        for (int e = threadIdx.x; e < 128 * 16; e += FT_THREADS) {
-            const int r = e >> 4, c = e & 15;
+        for (int e = threadIdx.x; e < 128 * (FT_HD / 8); e += FT_THREADS) {
+            const int r = e / (FT_HD / 8), c = e % (FT_HD / 8);
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < nrows) v = *(const uint4*)(q + (size_t)(qs0 + tok0 + r / G) * ldq + (size_t)(hk * G + r % G) * FT_HD + c * 8);
             *(uint4*)(smem + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
@@ -176,8 +176,9 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                         const int krow = ((page_of(ik) * 2 + 0) * nkv + hk) * KB_PAGE;
                         const uint32_t dst = s_kv + s * FT_STAGE_BYTES;
                         mbar_expect_tx(b_k_full + s * 8, FT_TILE_BYTES);
-                        tma_load_2d(dst, &kvmap, 0, krow, b_k_full + s * 8);
-                        tma_load_2d(dst + 8192, &kvmap, 64, krow, b_k_full + s * 8);
+#pragma unroll
+                        for (int h = 0; h < FT_HD / 64; h++)
+                            tma_load_2d(dst + h * 8192, &kvmap, h * 64, krow, b_k_full + s * 8);
                         ik++;
                         moved = true;
                     }
@@ -188,8 +189,9 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
                         const int vrow = ((page_of(iv) * 2 + 1) * nkv + hk) * KB_PAGE;
                         const uint32_t dst = s_kv + s * FT_STAGE_BYTES + FT_TILE_BYTES;
                         mbar_expect_tx(b_v_full + s * 8, FT_TILE_BYTES);
-                        tma_load_2d(dst, &kvmap, 0, vrow, b_v_full + s * 8);
-                        tma_load_2d(dst + 8192, &kvmap, 64, vrow, b_v_full + s * 8);
+#pragma unroll
+                        for (int h = 0; h < FT_HD / 64; h++)
+                            tma_load_2d(dst + h * 8192, &kvmap, h * 64, vrow, b_v_full + s * 8);
                         iv++;
                         moved = true;
                     }
@@ -213,14 +215,14 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && n_iter > 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64);                  // Q K^T: both K-major
-            constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);    // P V: V is MN-major
+            constexpr uint32_t idesc_o = umma_idesc_bf16(128, FT_HD) | (1u << 16);  // P V: V is MN-major
             bool ok = true;
             auto issue_s = [&](int j) {
                 const int s = j % FT_STAGES;
                 const uint32_t kt = s_kv + s * FT_STAGE_BYTES;
                 const uint32_t d = t_s + (uint32_t)(j & 1) * 64;
 #pragma unroll
-                for (int k = 0; k < 8; k++)          // 128 columns of the head = 2 blocks of 64 = 8 steps of 16
+                for (int k = 0; k < FT_HD / 16; k++) // the head's columns in blocks of 64 = steps of 16
                     umma_bf16(d, umma_desc_sw128(s_q + (k >> 2) * 16384 + (k & 3) * 32),
                               umma_desc_sw128(kt + (k >> 2) * 8192 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(b_s_full + (j & 1) * 8);
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             }
             if (rescale) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 32) {
+                for (int c0 = 0; c0 < FT_HD; c0 += 32) {
                     uint32_t ov[32];
                     tmem_ld_x32(t_o + lane_base + c0, ov);
                     tmem_ld_wait();
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             bf16* dst = out + (size_t)(qs0 + tok0 + (row_ok ? r / G : 0)) * ldo + (size_t)(hk * G + (row_ok ? r % G : 0)) * FT_HD;
 #pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
+            for (int c0 = 0; c0 < FT_HD; c0 += 32) {
                 uint32_t ov[32];
                 tmem_ld_x32(t_o + lane_base + c0, ov);
                 tmem_ld_wait();
@@ -404,28 +406,41 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
 }
 
 // grid_x = the most tiles of a sequence: ceil(longest q_len / (128 / G)) with G = nh / nkv <= 128
-extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int* slot, const int* q_start,
-                          const int* kv_len, int B, int nh, int nkv, int hd, float scale, int window, void* pool,
+template <int HD>
+static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, const int* slot,
+                          const int* q_start, const int* kv_len, int B, int nh, int nkv, float scale, int window,
                           const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st) {
-    if (B <= 0 || grid_x <= 0) return 0;
-    if (hd != FT_HD || nkv <= 0 || nh % nkv || nh / nkv > 128) return (int)cudaErrorInvalidValue;
-    if ((ldq % 8) || (ldo % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
-    CUtensorMap map;
-    int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
-    if (rc) return rc;
-    // 96 KB of tiles + barriers + what aligning the base to 1024 can cost when it is aligned to 128: two CTAs fit
-    const int sm = FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES + 256 + 768;
+    // tiles (Q and two stages of keys and values: 96 KB at head size 128) + barriers + what aligning the base to 1024
+    // can cost when it is aligned to 128: two CTAs fit an SM
+    const int sm = 128 * HD * 2 + FT_STAGES * 2 * 64 * HD * 2 + 256 + 768;
     static bool done = false;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(k_attn_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        cudaError_t e = cudaFuncSetAttribute(k_attn_tc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(k_attn_tc, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        e = cudaFuncSetAttribute(k_attn_tc<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
     dim3 grid(grid_x, nkv, B);
-    cudaError_t e = kb_launch(k_attn_tc, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot, q_start,
-                              kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table, table_stride, n_pages,
-                              status);
+    cudaError_t e = kb_launch(k_attn_tc<HD>, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot,
+                              q_start, kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table, table_stride,
+                              n_pages, status);
     return (int)e;
+}
+
+// grid_x = the most tiles of a sequence: ceil(longest q_len / (128 / G)) with G = nh / nkv <= 128; head size 64 or 128
+extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int* slot, const int* q_start,
+                          const int* kv_len, int B, int nh, int nkv, int hd, float scale, int window, void* pool,
+                          const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st) {
+    if (B <= 0 || grid_x <= 0) return 0;
+    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 128) return (int)cudaErrorInvalidValue;
+    if ((ldq % 8) || (ldo % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map;
+    int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
+    if (rc) return rc;
+    if (hd == 128)
+        return launch_attn_tc<128>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
+                                   table_stride, n_pages, grid_x, status, st);
+    return launch_attn_tc<64>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
+                              table_stride, n_pages, grid_x, status, st);
 }

@@ -158,7 +158,7 @@ def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages
         return True
     if ctx.graph:
         return False
-    if hd == 128 and g <= 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+    if g <= 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
         # prompt-sized steps: the tcgen05 kernel (S and O in tensor memory)
         K.attn_tc(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,
                   grid_x=-(-ctx.max_q // (128 // g)), status=ctx.status)

@@ -321,11 +321,11 @@ def attn_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tenso
 def attn_tc(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
             scale: float, window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, grid_x: int,
             status: torch.Tensor) -> None:
-    """tcgen05 attention for prompt-sized steps (bf16, head size 128): grid_x = ceil(most rows of a sequence /
+    """tcgen05 attention for prompt-sized steps (bf16, head size 64 or 128): grid_x = ceil(most rows of a sequence /
     (128 // (nh / nkv)))"""
     _need_cuda(q, out, pool, table)
     assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
-    assert pool.is_contiguous() and hd == 128
+    assert pool.is_contiguous() and hd in (64, 128)
     _check(load().kb_attn_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(slot), _p(q_start), _p(kv_len), B, nh, nkv,
                              hd, float(scale), int(window), _p(pool), _p(table), table.stride(0), n_pages, grid_x,
                              _p(status), _stream()), "attn_tc")

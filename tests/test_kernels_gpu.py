@@ -260,17 +260,19 @@ def test_gemm_tc_finishes_swiglu_in_its_epilogue(K, M, F, K_, bn):
     assert _rel(h.float(), ref) < 1.5e-2
 
 
-@pytest.mark.parametrize("nh,nkv,window", [(20, 4, 0), (3, 1, 0), (8, 8, 0), (10, 2, 64), (16, 1, 0), (6, 2, 100)])
-def test_attention_tc_prefill(K, nh, nkv, window):
+@pytest.mark.parametrize("nh,nkv,window,hd", [(20, 4, 0, 128), (3, 1, 0, 128), (8, 8, 0, 128), (10, 2, 64, 128),
+                                              (16, 1, 0, 128), (6, 2, 100, 128), (5, 1, 0, 64), (8, 8, 0, 64),
+                                              (14, 2, 100, 64), (12, 1, 64, 64)])
+def test_attention_tc_prefill(K, nh, nkv, window, hd):
     # whole prompts, a chunk that continues an earlier part, single rows, lengths at and around page edges
-    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, 128, [64, 1, 130, 33, 7], [64, 129, 130, 97, 200],
+    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, hd, [64, 1, 130, 33, 7], [64, 129, 130, 97, 200],
                          window, seed=nh)
     assert err < 1e-2
     # one far key among hundreds decides a row (the lazy maximum has to follow it)
-    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, 128, [40, 3], [700, 65], window=0, seed=nh + 1,
+    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, hd, [40, 3], [700, 65], window=0, seed=nh + 1,
                          boost=(0, 39, 5))
     assert err < 1e-2
-    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, 128, [300], [300], window=window, seed=nh + 2,
+    err = _run_attention(K, "tc", torch.bfloat16, nh, nkv, hd, [300], [300], window=window, seed=nh + 2,
                          boost=(0, 299, 250))
     assert err < 1e-2
 
@@ -427,7 +429,8 @@ def test_rope_store_against_plain(K, T, nh, nkv, hd, rot, planes):
 
 @pytest.mark.parametrize("kind,hd,dtype", [("generic", 48, torch.float32), ("generic", 128, torch.bfloat16),
                                            ("prefill", 64, torch.bfloat16), ("decode", 128, torch.bfloat16),
-                                           ("decode", 64, torch.bfloat16), ("tc", 128, torch.bfloat16)])
+                                           ("decode", 64, torch.bfloat16), ("tc", 128, torch.bfloat16),
+                                           ("tc", 64, torch.bfloat16)])
 def test_attention_window_edge(K, kind, hd, dtype):
     """a key that stands out, placed on the last position a row may still see (pos - window + 1) and on the first it
     may not (pos - window): an off-by-one at the window's edge then changes the output grossly, not by a few per cent"""
