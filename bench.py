@@ -125,19 +125,20 @@ def prefill_flops(mc, T: int) -> float:
     return L * (T * per_tok + attn) + 2.0 * E * mc.vocab_size  # the head runs on one row
 
 
-def bench_prefill(eng, warmup: int, iters: int):
+def bench_prefill(eng, warmup: int, iters: int, tokens: int = 0):
     import random
     import torch
     from kindi_b200.engine.batch import StepEntry
     rng = random.Random(3)
-    ids = tuple(rng.randrange(eng.spec.vocab_size) for _ in range(PREFILL_TOKENS))
+    tokens = tokens or PREFILL_TOKENS
+    ids = tuple(rng.randrange(eng.spec.vocab_size) for _ in range(tokens))
     times = []
     for i in range(warmup + iters):
         slot = eng.alloc()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         a.record()
-        eng.step([StepEntry(slot, ids, (PREFILL_TOKENS - 1,))])
+        eng.step([StepEntry(slot, ids, (tokens - 1,))])
         b.record()
         torch.cuda.synchronize()
         if i >= warmup:
@@ -245,7 +246,9 @@ def main(argv=None) -> int:
                          "Python entry point (the 16B-class configuration's workload)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
-    ap.add_argument("--prefill-only", action="store_true", help="measure only the 2048-token prefill (for profiling)")
+    ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill (for profiling)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="prompt length of --prefill-only (the full run always measures 2048 tokens)")
     a = ap.parse_args(argv)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -270,10 +273,10 @@ def main(argv=None) -> int:
     max_b = max(a.batch, 1 if a.no_points else max(point_batches))
     ctx = max_b * (a.context + a.steps * 2 + a.warmup + 256) + PREFILL_TOKENS + 64
     if a.prefill_only:
-        eng = build_engine(a.layers, PREFILL_TOKENS + 128, 2, base)
-        pms = bench_prefill(eng, 2, max(1, min(a.steps, 3)))
-        print(json.dumps({"prefill_only": True, "layers": a.layers, "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
-                          "value": round(PREFILL_TOKENS * 1000.0 / pms, 1)}))
+        eng = build_engine(a.layers, a.prefill_tokens + 128, 2, base)
+        pms = bench_prefill(eng, 2, max(1, min(a.steps, 3)), a.prefill_tokens)
+        print(json.dumps({"prefill_only": True, "layers": a.layers, "tokens": a.prefill_tokens, "ms": round(pms, 3),
+                          "value": round(a.prefill_tokens * 1000.0 / pms, 1)}))
         return 0
     eng = build_engine(a.layers, ctx, max_b, base)
     for g in eng.cache.groups:
