@@ -259,8 +259,10 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
         // ------------------------------------------------------------ softmax: thread = row = TMEM lane
         const int r = warp * 32 + lane;
         const bool row_ok = r < nrows;
-        const int p_row = row_ok ? pos0 + tok0 + r / G : -1;
-        const int lo_row = (window > 0 && p_row - window + 1 > 0) ? p_row - window + 1 : 0;
+        // (a padding row, whose query is zero and whose result is not written, sees every key: with a span of its own
+        // it would take its whole warp through the masked branch at every page)
+        const int p_row = row_ok ? pos0 + tok0 + r / G : 0x3fffffff;
+        const int lo_row = (row_ok && window > 0 && p_row - window + 1 > 0) ? p_row - window + 1 : 0;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
