@@ -102,7 +102,8 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + FT_Q_BYTES + FT_STAGES * FT_STAGE_BYTES +
                                                         (4 * FT_STAGES + 4) * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, hk = blockIdx.y;
+    // grid: (key/value heads, tiles, sequences): the longest tiles of every head start first, the shortest fill the end
+    const int b = blockIdx.z, hk = blockIdx.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < FT_STAGES; s++) {
@@ -126,8 +127,8 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
     const int pos0 = kvl - qlen;
     const int TOK = 128 / G;                         // whole tokens per CTA
     const int n_tiles = (qlen + TOK - 1) / TOK;
-    const bool active = (int)blockIdx.x < n_tiles;   // uniform over the CTA
-    const int tile = n_tiles - 1 - (int)blockIdx.x;  // the longest tiles first
+    const bool active = (int)blockIdx.y < n_tiles;   // uniform over the CTA
+    const int tile = n_tiles - 1 - (int)blockIdx.y;  // the longest tiles first
     const int tok0 = tile * TOK;
     const int ntok = active ? min(TOK, qlen - tok0) : 0;
     const int nrows = ntok * G;
@@ -137,21 +138,36 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
     const int pg_lo = lo_cta / KB_PAGE, pg_hi = p_last / KB_PAGE;
     const int n_iter = active ? pg_hi - pg_lo + 1 : 0;
 
-    // ---- Q into shared memory: two K-blocks of [128 rows][64 columns], rows of 128 bytes, 128-byte swizzle
-    if (active) {
-        for (int e = threadIdx.x; e < 128 * (FT_HD / 8); e += FT_THREADS) {
-            const int r = e / (FT_HD / 8), c = e % (FT_HD / 8);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < nrows) v = *(const uint4*)(q + (size_t)(qs0 + tok0 + r / G) * ldq + (size_t)(hk * G + r % G) * FT_HD + c * 8);
-            *(uint4*)(smem + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();                                 // the barriers and the tensor memory's address are there
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t t_s = tmem, t_o = tmem + 128;     // S buffers at columns 0 and 64, O at 128..255
+
+    // ---- Q into shared memory: two K-blocks of [128 rows][64 columns], rows of 128 bytes, 128-byte swizzle. The five
+    // warps that do not load keys and values bring it, every load in flight before the first store (one trip to the
+    // L2 instead of one a piece), while the producer warp already fetches the first pages.
+    if (warp != 4) {
+        if (active) {
+            constexpr int QT = FT_THREADS - 32, QV = 128 * (FT_HD / 8), QN = (QV + QT - 1) / QT;
+            const int qt = warp < 4 ? (int)threadIdx.x : (int)threadIdx.x - 32;
+            uint4 v[QN];
+#pragma unroll
+            for (int i = 0; i < QN; i++) {
+                const int e = qt + i * QT, r = e / (FT_HD / 8), c = e % (FT_HD / 8);
+                v[i] = make_uint4(0, 0, 0, 0);
+                if (e < QV && r < nrows)
+                    v[i] = *(const uint4*)(q + (size_t)(qs0 + tok0 + r / G) * ldq + (size_t)(hk * G + r % G) * FT_HD + c * 8);
+            }
+#pragma unroll
+            for (int i = 0; i < QN; i++) {
+                const int e = qt + i * QT, r = e / (FT_HD / 8), c = e % (FT_HD / 8);
+                if (e < QV) *(uint4*)(smem + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v[i];
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(FT_THREADS - 32) : "memory");
+    }
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
@@ -423,7 +439,7 @@ static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* 
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    dim3 grid(grid_x, nkv, B);
+    dim3 grid(nkv, grid_x, B);
     cudaError_t e = kb_launch(k_attn_tc<HD>, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot,
                               q_start, kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table, table_stride,
                               n_pages, status);
@@ -435,6 +451,7 @@ extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int*
                           const int* kv_len, int B, int nh, int nkv, int hd, float scale, int window, void* pool,
                           const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st) {
     if (B <= 0 || grid_x <= 0) return 0;
+    if (grid_x > 65535 || B > 65535) return (int)cudaErrorInvalidValue;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 128) return (int)cudaErrorInvalidValue;
     if ((ldq % 8) || (ldo % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
     CUtensorMap map;
