@@ -56,15 +56,21 @@ def _splits_for(m: int, n: int, k: int, bn: int) -> int:
 
 @functools.lru_cache(maxsize=4096)
 def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
-    """(columns of a tile, row tiles per unit) for a prompt-sized product: the pair with the least estimated time.
-    A K block of a unit costs what is slower, its MMAs (0.276 us for 128 x 256 x 64) or bringing its operand tiles
-    from the L2 (about 1.15 ns per operand row); two row tiles over one weight tile halve the weight traffic per
-    FLOP but leave the epilogue exposed; units fill the persistent CTAs in rounds and a partly filled round costs a
-    whole one."""
+    """(kind, columns of a tile, variant) for a prompt-sized product: what has the least estimated time.
+
+    kind "tc" (variant = row tiles per unit, 1 or 2): one CTA per unit. A K block of a unit costs what is slower, its
+    MMAs (0.276 us for 128 x 256 x 64) or bringing its operand tiles from the L2 (about 1.15 ns per operand row); two
+    row tiles over one weight tile halve the weight traffic per FLOP but leave the epilogue exposed; units fill the
+    persistent CTAs in rounds and a partly filled round costs a whole one.
+
+    kind "pair" (variant = True: the K blocks of all tiles dealt out evenly, False: tile by tile): two CTAs per
+    256-row tile, each with half of the weight tile. Measured 0.39 us per K block of 256 x 256 x 64 (the rate of the
+    library's product under the power limit); dealing out K blocks costs about 10 us for the tiles that two pairs
+    finish together."""
     if n <= 64:
-        return 64, 1
+        return "tc", 64, 1
     kb = -(-k // 64)
-    best, best_cost = (128, 1), None
+    best, best_cost = ("tc", 128, 1), None
     for mt in ((1, 2) if m >= 256 else (1,)):
         for bn in (256, 240, 224, 208, 192, 176, 160, 144, 128):
             if swiglu and bn % 32:
@@ -74,8 +80,42 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
             epilogue = (0.02 if mt == 2 else 0.004) * bn * mt
             cost = -(-units // N_SM) * (kb * t_kb + epilogue)
             if best_cost is None or cost < best_cost:
-                best, best_cost = (bn, mt), cost
+                best, best_cost = ("tc", bn, mt), cost
+    if m >= 512:
+        pairs = N_SM // 2
+        for bn in (256, 192, 128):
+            units = -(-m // 256) * -(-n // bn)
+            t_kb = max(0.39 * bn / 256.0, 1.15e-3 * (128 + bn // 2))
+            cost = -(-units // pairs) * (kb * t_kb + 1.5)
+            if cost < best_cost:
+                best, best_cost = ("pair", bn, False), cost
+            if not swiglu and units >= pairs:
+                cost = units * kb / pairs * t_kb + 10.0
+                if cost < best_cost:
+                    best, best_cost = ("pair", bn, True), cost
     return best
+
+
+_PAIR_SCRATCH = {}         # device -> (partial tiles, flags): scratch of tiles that two pairs of SMs finish together
+
+
+def _prefill_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, swiglu: bool) -> None:
+    m, k = a.shape
+    n = w.shape[0]
+    kind, bn, variant = _prefill_tile(m, n, k, swiglu)
+    if kind == "tc":
+        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=status, swiglu=swiglu, mt=variant)
+        return
+    part = flags = None
+    if variant:
+        tiles = -(-m // 256) * -(-n // bn)
+        have = _PAIR_SCRATCH.get(a.device)
+        if have is None or have[0].numel() < tiles * 256 * bn or have[1].numel() < 8 * tiles:
+            have = (torch.empty(tiles * 256 * bn, dtype=torch.float32, device=a.device),
+                    torch.zeros(8 * tiles, dtype=torch.int32, device=a.device))
+            _PAIR_SCRATCH[a.device] = have
+        part, flags = have
+    K.gemm_pair(a, w, out, bn=bn, status=status, swiglu=swiglu, part=part, flags=flags)
 
 
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
@@ -85,8 +125,7 @@ def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
     if m <= SMALL_M:
         K.gemm_tc(a, w, out, swap=True, bn=_swap_bn(m), splits=1, status=status)
     else:
-        bn, mt = _prefill_tile(m, n, a.shape[1])
-        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=status, mt=mt)
+        _prefill_product(a, w, out, status, False)
     return True
 
 
@@ -103,8 +142,7 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
         K.gemm_tc(a, w, out, swap=True, bn=bn, splits=want, status=status)
         return out
     out = torch.empty((1, m, n), dtype=torch.float32, device=a.device)
-    bn, mt = _prefill_tile(m, n, k)
-    K.gemm_tc(a, w, out[0], swap=False, bn=bn, splits=1, status=status, mt=mt)
+    _prefill_product(a, w, out[0], status, False)
     return out
 
 
@@ -114,8 +152,7 @@ def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor
     m, n = a.shape[0], w_grouped.shape[0]
     if m <= SMALL_M or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
         return False
-    bn, mt = _prefill_tile(m, n, a.shape[1], swiglu=True)
-    K.gemm_tc(a, w_grouped, out, swap=False, bn=bn, splits=1, status=status, swiglu=True, mt=mt)
+    _prefill_product(a, w_grouped, out, status, True)
     return True
 
 
@@ -123,9 +160,9 @@ _SK_SCRATCH = {}           # (device, tiles, bn) -> (partial tiles, flags): scra
 
 
 def reset_scratch() -> None:
-    """lower every flag of the decode gate/up product's scratch: after a step whose kernels reported an error (a wait
+    """lower every flag of the products' scratch (decode gate/up, tiles shared by two pairs of SMs): after a step whose kernels reported an error (a wait
     that ran out can leave a flag raised, which the next step would take for a partial tile that is there)"""
-    for _, flags in _SK_SCRATCH.values():
+    for _, flags in list(_SK_SCRATCH.values()) + list(_PAIR_SCRATCH.values()):
         flags.zero_()
 
 

@@ -42,6 +42,8 @@ _SIGS = {
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_longlong, c_void_p, c_void_p, c_int, c_int],
     "kb_gemm_tc_splits": [c_int, c_int],
+    "kb_gemm_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                     c_void_p, c_int, c_void_p, c_void_p],
     "kb_gemm_swiglu_decode": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                               c_void_p, c_void_p, c_void_p],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -251,6 +253,32 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, 
         stride, ldc = 0, N
     _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, 1 if swap else 0,
                              bn, splits, stride, _p(status), _stream(), 1 if swiglu else 0, mt), "gemm_tc")
+
+
+def gemm_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bn: int, status: torch.Tensor,
+              swiglu: bool = False, part: Optional[torch.Tensor] = None, flags: Optional[torch.Tensor] = None) -> None:
+    """out = a[M, K] @ w[N, K]^T by pairs of SMs (tcgen05 with cta_group::2: a pair computes 256 rows x bn columns,
+    each CTA holding half of the weight tile), bf16 in, fp32 accumulate, ``out`` [M, N] bf16 or fp32; bn 64, 128, 192
+    or 256. ``swiglu``: as for gemm_tc, ``out`` is the bf16 [M, N / 2] result silu(gate) * up. With ``part`` (fp32, at
+    least tiles * 256 * bn elements, tiles = ceil(M / 256) * ceil(N / bn)) and ``flags`` (int32 zeros, 8 a tile) the
+    K blocks of all tiles are dealt out evenly to the pairs and a tile may be finished by two of them"""
+    _need_cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.is_contiguous() and bn in (64, 128, 192, 256)
+    if swiglu:
+        assert out.shape == (M, N // 2) and out.dtype == torch.bfloat16 and N % 32 == 0
+        ldc = N // 2
+    else:
+        assert out.shape == (M, N)
+        ldc = N
+    if part is not None:
+        tiles = -(-M // 256) * -(-N // bn)
+        assert part.dtype == torch.float32 and part.numel() >= tiles * 256 * bn and part.is_contiguous()
+        assert flags.dtype == torch.int32 and flags.numel() >= 8 * tiles and flags.is_contiguous()
+    _check(load().kb_gemm_pair(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, bn, _p(status),
+                               _stream(), 1 if swiglu else 0, _p(part), _p(flags)), "gemm_pair")
 
 
 def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, bn: int, part: torch.Tensor,

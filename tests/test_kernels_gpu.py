@@ -277,6 +277,42 @@ def test_attention_tc_prefill(K, nh, nkv, window, hd):
     assert err < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 256), (2048, 2560, 1096, 256), (300, 700, 200, 192),
+                                       (513, 1000, 136, 128), (1000, 520, 264, 64), (1900, 2500, 520, 192),
+                                       (2048, 3584, 200, 256), (100, 96, 72, 128), (2304, 2560, 328, 256)])
+def test_gemm_pair_of_sms(K, M, N, K_, bn):
+    """the product on pairs of SMs (tcgen05 with cta_group::2), tile by tile and with the K blocks of all tiles dealt
+    out evenly (tiles finished by two pairs), both output types, and SwiGLU in the epilogue"""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K_)
+    a = torch.randn(M, K_, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K_, device="cuda", generator=g).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    st = _status()
+    tiles = -(-M // 256) * -(-N // bn)
+    part = torch.full((tiles * 256 * bn,), float("nan"), device="cuda")
+    flags = torch.zeros(8 * tiles, dtype=torch.int32, device="cuda")
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 5e-3)):
+        out = torch.full((M, N), float("nan"), device="cuda", dtype=dtype)
+        K.gemm_pair(a, w, out, bn=bn, status=st)
+        assert int(st.item()) == 0
+        assert _rel(out.float(), ref) < tol
+        for _ in range(2):          # twice: the flags of the first call have been lowered
+            out2 = torch.full((M, N), float("nan"), device="cuda", dtype=dtype)
+            K.gemm_pair(a, w, out2, bn=bn, status=st, part=part, flags=flags)
+            assert int(st.item()) == 0 and int(flags.abs().sum().item()) == 0
+            assert _rel(out2.float(), ref) < tol
+    if N % 32 == 0:
+        F = N // 2
+        wg, wu = w[:F], w[F:]
+        wgu = torch.stack([wg.view(F // 16, 16, K_), wu.view(F // 16, 16, K_)], dim=1).reshape(N, K_).contiguous()
+        h = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+        K.gemm_pair(a * 0.1, wgu, h, bn=bn, status=st, swiglu=True)
+        assert int(st.item()) == 0
+        gg = (a * 0.1).double() @ wg.double().T
+        uu = (a * 0.1).double() @ wu.double().T
+        assert _rel(h.float(), gg / (1 + torch.exp(-gg)) * uu) < 1e-2
+
+
 @pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 128), (2048, 2560, 1096, 160), (300, 700, 200, 192),
                                        (513, 1000, 136, 224), (1000, 520, 264, 256), (2048, 2560, 328, 144),
                                        (300, 400, 72, 176), (2048, 3584, 200, 208), (257, 500, 136, 240)])
