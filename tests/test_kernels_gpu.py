@@ -313,6 +313,41 @@ def test_gemm_pair_of_sms(K, M, N, K_, bn):
         assert _rel(h.float(), gg / (1 + torch.exp(-gg)) * uu) < 1e-2
 
 
+def test_prompt_products_as_the_engine_chooses_them(K):
+    """the dispatch of prompt-sized products at the benchmark's layer sizes: the down product goes to pairs of SMs with
+    its K blocks dealt out evenly (scratch and flags kept by the dispatcher, reused by the next call), gate/up to pairs
+    tile by tile with SwiGLU in the epilogue, QKV to one CTA a unit; all against float64 products"""
+    from kindi_b200.kernels import fast
+    assert fast._prefill_tile(2048, 2560, 10496) == ("pair", 256, True)
+    assert fast._prefill_tile(2048, 20992, 2560, True) == ("pair", 256, False)
+    assert fast._prefill_tile(2048, 3584, 2560)[0] == "tc"
+    g = torch.Generator(device="cuda").manual_seed(5)
+    st = _status()
+    M = 2048
+    for N, K_ in ((2560, 10496), (3584, 2560)):
+        a = (torch.randn(M, K_, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(N, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        ref = a.float() @ w.float().T               # (float32 on the GPU: float64 at this size takes too long)
+        for _ in range(2):
+            planes = fast.gemm_planes(a, w, st)
+            assert planes is not None and int(st.item()) == 0
+            assert _rel(planes.sum(0), ref) < 2e-5
+        out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+        assert fast.gemm_rows(a, w, out, st) and int(st.item()) == 0
+        assert _rel(out.float(), ref) < 5e-3
+    F, K_ = 9472, 1024
+    a = (torch.randn(M, K_, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    wg = (torch.randn(F, K_, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(F, K_, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wgu = torch.stack([wg.view(F // 16, 16, K_), wu.view(F // 16, 16, K_)], dim=1).reshape(2 * F, K_).contiguous()
+    assert fast._prefill_tile(M, 2 * F, K_, True)[0] == "pair"
+    h = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+    assert fast.gemm_swiglu_rows(a, wgu, h, st) and int(st.item()) == 0
+    gg, uu = a.float() @ wg.float().T, a.float() @ wu.float().T
+    assert _rel(h.float(), gg / (1 + torch.exp(-gg)) * uu) < 1e-2
+    assert all(int(f.abs().sum().item()) == 0 for _, f in fast._PAIR_SCRATCH.values())
+
+
 @pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 128), (2048, 2560, 1096, 160), (300, 700, 200, 192),
                                        (513, 1000, 136, 224), (1000, 520, 264, 256), (2048, 2560, 328, 144),
                                        (300, 400, 72, 176), (2048, 3584, 200, 208), (257, 500, 136, 240)])
