@@ -64,8 +64,8 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
     persistent CTAs in rounds and a partly filled round costs a whole one.
 
     kind "pair" (variant = True: the K blocks of all tiles dealt out evenly, False: tile by tile): two CTAs per
-    256-row tile, each with half of the weight tile. Measured 0.39 us per K block of 256 x 256 x 64 (the rate of the
-    library's product under the power limit); dealing out K blocks costs about 10 us for the tiles that two pairs
+    256-row tile, each with half of the weight tile. Measured 0.36-0.39 us per K block of 256 x 256 x 64 (the rate of
+    the library's product under the power limit); dealing out K blocks costs about 10 us for the tiles that two pairs
     finish together."""
     if n <= 64:
         return "tc", 64, 1
@@ -85,11 +85,13 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
         pairs = N_SM // 2
         for bn in (256, 192, 128):
             units = -(-m // 256) * -(-n // bn)
-            t_kb = max(0.39 * bn / 256.0, 1.15e-3 * (128 + bn // 2))
+            t_kb = max(0.37 * bn / 256.0, 0.33)         # (narrower tiles were not measured faster than 0.33 us)
             cost = -(-units // pairs) * (kb * t_kb + 1.5)
             if cost < best_cost:
                 best, best_cost = ("pair", bn, False), cost
-            if not swiglu and units >= pairs:
+            # (dealt out, the pairs that share an operand tile read it some K blocks apart in time: both operands have
+            # to stay in the L2 meanwhile, or the product waits for DRAM: 5120 x 13824 weights, 288 us against 226)
+            if not swiglu and units >= pairs and (m + n) * k * 2 <= 100e6:
                 cost = units * kb / pairs * t_kb + 10.0
                 if cost < best_cost:
                     best, best_cost = ("pair", bn, True), cost
