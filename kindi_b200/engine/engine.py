@@ -284,6 +284,7 @@ class _DecodeGraph:
         self.engine = engine
         n = ps.meta.size
         self.pin = torch.empty(n, dtype=torch.int32, pin_memory=True)
+        self.pin_np = self.pin.numpy()           # the same memory, written without a tensor operation
         self.meta = torch.zeros(n, dtype=torch.int32, device=engine.device)
         self.meta.copy_(torch.from_numpy(ps.meta))
         self.copied = None
@@ -310,11 +311,12 @@ class _DecodeGraph:
         K.add_launches(-self.launches)
 
     def replay(self, ps: PackedStep) -> torch.Tensor:
-        if self.copied is not None:
+        if self.copied is None:
+            self.copied = torch.cuda.Event()
+        else:
             self.copied.synchronize()            # the pinned buffer is free again
-        self.pin.copy_(torch.from_numpy(ps.meta))
+        self.pin_np[:] = ps.meta
         self.meta.copy_(self.pin, non_blocking=True)
-        self.copied = torch.cuda.Event()
         self.copied.record()
         self.graph.replay()
         K.add_launches(self.launches)
