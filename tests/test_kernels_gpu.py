@@ -296,11 +296,14 @@ def test_gemm_pair_of_sms(K, M, N, K_, bn):
         K.gemm_pair(a, w, out, bn=bn, status=st)
         assert int(st.item()) == 0
         assert _rel(out.float(), ref) < tol
-        for _ in range(2):          # twice: the flags of the first call have been lowered
+        first = None
+        for _ in range(2):          # twice: the flags of the first call have been lowered, and the bits are the same
             out2 = torch.full((M, N), float("nan"), device="cuda", dtype=dtype)
             K.gemm_pair(a, w, out2, bn=bn, status=st, part=part, flags=flags)
             assert int(st.item()) == 0 and int(flags.abs().sum().item()) == 0
             assert _rel(out2.float(), ref) < tol
+            assert first is None or torch.equal(first, out2)
+            first = out2
     if N % 32 == 0:
         F = N // 2
         wg, wu = w[:F], w[F:]
