@@ -1,0 +1,41 @@
+"""The choice of kernel and tile for prompt-sized products (pure arithmetic, no GPU): what the kernels accept, and the
+rules that measurements gave."""
+import itertools
+
+from kindi_b200.kernels import fast
+
+TC_WIDTHS = {64, 128, 144, 160, 176, 192, 208, 224, 240, 256}
+PAIR_WIDTHS = {64, 128, 192, 256}
+
+
+def test_every_choice_is_one_the_kernels_take():
+    for m, n, k, sw in itertools.product((33, 100, 256, 511, 512, 700, 2048, 5000, 9314), (48, 96, 520, 2560, 3584, 20992, 51200),
+                                         (64, 200, 2560, 10496, 25600), (False, True)):
+        if sw and n % 32:
+            continue
+        kind, bn, variant = fast._prefill_tile(m, n, k, sw)
+        if kind == "tc":
+            assert bn in TC_WIDTHS and variant in (1, 2)
+            assert variant == 1 or m >= 256
+            assert not sw or bn % 32 == 0 or n <= 64
+        else:
+            assert kind == "pair" and bn in PAIR_WIDTHS and variant in (True, False)
+            assert m >= 512                                   # a pair's tile has 256 rows
+            if variant:
+                # K blocks dealt out: never with SwiGLU in the epilogue, only when a stretch is at least a tile long
+                # and while both operands fit the L2
+                assert not sw
+                assert -(-m // 256) * -(-n // bn) >= fast.N_SM // 2
+                assert (m + n) * k * 2 <= 100e6
+
+
+def test_choices_at_the_benchmark_sizes():
+    # 3B-shaped layer, a 2048-token prompt: what was measured fastest
+    assert fast._prefill_tile(2048, 20992, 2560, True) == ("pair", 256, False)      # gate/up
+    assert fast._prefill_tile(2048, 2560, 10496) == ("pair", 256, True)             # down
+    assert fast._prefill_tile(2048, 3584, 2560)[0] == "tc"                          # QKV
+    assert fast._prefill_tile(2048, 2560, 2560)[0] == "tc"                          # O
+    # the larger layers' down products do not fit the L2: not dealt out
+    for f in (13824, 25600):
+        kind, _, variant = fast._prefill_tile(2048, 5120, f)
+        assert not (kind == "pair" and variant)
