@@ -122,9 +122,32 @@ class SequenceCache:
             last: Dict[Tuple[int, int], int] = {}
             for s, b, pg in dirty:
                 last[(s, b)] = pg
-            idx = torch.tensor([s * self.n_pages + b for (s, b) in last], dtype=torch.int64)
-            val = torch.tensor(list(last.values()), dtype=torch.int32)
-            g.table.view(-1).index_copy_(0, idx.to(self.device), val.to(self.device))
+            n = len(last)
+            if self.device.type != "cuda":
+                idx = torch.tensor([s * self.n_pages + b for (s, b) in last], dtype=torch.int64)
+                val = torch.tensor(list(last.values()), dtype=torch.int32)
+                g.table.view(-1).index_copy_(0, idx, val)
+                continue
+            # one copy from pinned memory (places, then pages) instead of two from pageable memory, each of which
+            # would hold the host up for tens of microseconds before the step's first kernel
+            stage = self._stage(2 * n)
+            stage[:n] = torch.tensor([s * self.n_pages + b for (s, b) in last], dtype=torch.int64)
+            stage[n:2 * n] = torch.tensor(list(last.values()), dtype=torch.int64)
+            dev = stage[:2 * n].to(self.device, non_blocking=True)
+            self._stage_free.record()
+            g.table.view(-1).index_copy_(0, dev[:n], dev[n:].to(torch.int32))
+
+    def _stage(self, n: int) -> torch.Tensor:
+        """pinned int64 staging memory of at least n elements, free to be written (the copy out of it that was issued
+        last has finished)"""
+        buf = getattr(self, "_stage_buf", None)
+        if buf is None:
+            self._stage_free = torch.cuda.Event()
+        else:
+            self._stage_free.synchronize()
+        if buf is None or buf.numel() < n:
+            buf = self._stage_buf = torch.empty(max(256, 2 * n), dtype=torch.int64, pin_memory=True)
+        return buf
 
     # ------------------------------------------------------------------ views for the parts
     def kv_view(self, entry: int):
