@@ -8,6 +8,7 @@ launch.
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_int, c_float, c_void_p, c_longlong
 from typing import Optional
 
@@ -130,13 +131,14 @@ def _p(t: Optional[torch.Tensor]):
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None) or torch.cuda.current_device
 
 
 def _stream():
     """the current stream's handle (asked of torch directly: building a Stream object costs several microseconds,
     which a step of a hundred launches feels)"""
     if _raw_stream is not None:
-        return _raw_stream(torch.cuda.current_device())
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -300,6 +302,7 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
            "gemm_swiglu_decode")
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_tc_splits(K: int, wanted: int) -> int:
     return load().kb_gemm_tc_splits(K, wanted)
 
