@@ -103,15 +103,15 @@ class ClockSampler:
 
 def build_engine(layers: int, ctx: int, max_batch: int, base=None):
     import torch
-    from kindi_b200.config import ModelConfig, architecture
+    from kindi_b200.config import model_from_config
     from kindi_b200.engine.engine import Engine
-    from kindi_b200.parts.model import expected_tensors
+    from kindi_b200.parts.model import expected_tensors, tensor_inits
     from kindi_b200.weights.random_init import random_tensors
     cfg = dict(base or CONFIG_3B)
     cfg["num_hidden_layers"] = layers
-    mc = ModelConfig.from_dict(cfg)
-    spec = architecture(mc.architecture).build_spec(mc)
-    tensors = random_tensors(expected_tensors(spec), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
+    mc, spec = model_from_config(cfg)
+    tensors = random_tensors(expected_tensors(spec), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0",
+                             inits=tensor_inits(spec))
     eng = Engine(spec=spec, tensors=tensors, ctx=ctx, dtype="bfloat16", max_batch=max_batch)
     eng.config = mc
     return eng

@@ -13,8 +13,8 @@ of this package; there is no CPU or library fallback.
 """
 __version__ = "0.1.0"
 
-from .config import (ConfigError, EngineConfig, GREEDY, ModelConfig, ModelSpec, PartSpec, SamplingParams,
-                     ScheduleEntry, register_architecture, register_part)
+from .config import (ConfigError, ConfigReader, EngineConfig, GREEDY, LayerSpec, ModelSpec, PartSpec, SamplingParams,
+                     ScheduleEntry, model_from_config, model_from_dir, register_architecture, register_part)
 
 
 def __getattr__(name):

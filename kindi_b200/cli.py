@@ -122,16 +122,17 @@ def cmd_bench(a):
 def cmd_info(a):
     print("kindi_b200 %s" % __version__)
     if a.model:
-        from .config.model_config import ModelConfig
-        from .config.registry import architecture
+        import dataclasses
+        import math
+        from .config.registry import model_from_dir
         from .parts.model import cache_needs, expected_tensors
-        cfg = ModelConfig.from_dir(a.model)
-        spec = architecture(cfg.architecture).build_spec(cfg)
-        for k, v in sorted(cfg.to_dict().items()):
+        cfg, spec = model_from_dir(a.model)
+        shown = dataclasses.asdict(cfg) if dataclasses.is_dataclass(cfg) else dict(cfg)
+        for k, v in sorted(shown.items()):
             print("  %-24s %s" % (k, v))
         shapes = expected_tensors(spec)
-        n = sum(int.__mul__(*s) if len(s) == 2 else s[0] for s in shapes.values())
-        print("model: %s, %d layers, %d tensors, %.3f B parameters" % (cfg.architecture, len(spec.layers),
+        n = sum(math.prod(s) for s in shapes.values())
+        print("model: %s, %d layers, %d tensors, %.3f B parameters" % (spec.architecture, len(spec.layers),
                                                                         len(shapes), n / 1e9))
         import torch
         from .cache.sequence_cache import SequenceCache

@@ -1,32 +1,41 @@
 """One registry from an architecture's name to its model, and one from a part's kind to its class.
 
 The reference picks its engine by a manifest string (``kindi/server.py:87-97``) after recognising the file's
-architecture (``kindi/nanbeige_cli.py:11-15``: ``general.architecture == "llama"``); here config.json's
-``architectures[0]`` (or ``model_type``) picks an ``Architecture``: a function from the typed configuration to a
-``ModelSpec``. Parts (mixers, feed-forwards, norms, position encodings, block arrangements) are looked up by kind
-when the model is built, so a new part is one ``register_part`` call and needs no change to this package.
+architecture (``kindi/nanbeige_cli.py:11-15``: ``general.architecture == "llama"``), and each engine class reads its
+own configuration. Here config.json's ``architectures[0]`` (or ``model_type``) picks an ``Architecture``: a reader of
+that architecture's own config.json keys (``read_config``: raw JSON object -> its typed configuration) and a function
+from that configuration to a ``ModelSpec`` (``build_spec``). Nothing is parsed before the name is looked up, so an
+architecture with other keys (no heads, another activation) is a registry entry, not a change to this package.
+Parts (embeddings, mixers, feed-forwards, norms, position encodings, block arrangements, heads) are looked up by
+kind when the model is built, so a new part is one ``register_part`` call.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, Tuple
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
+
+from .model_config import architecture_name, read_config_json
 
 
 @dataclass(frozen=True)
 class Architecture:
     name: str
-    build_spec: Callable        # (ModelConfig) -> ModelSpec
+    build_spec: Callable        # (the architecture's configuration) -> ModelSpec
+    read_config: Callable       # (raw JSON object of config.json) -> the architecture's configuration
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 _PARTS: Dict[Tuple[str, str], type] = {}
-PART_CATEGORIES = ("block", "mixer", "feed_forward", "norm", "position")
+PART_CATEGORIES = ("embedding", "block", "mixer", "feed_forward", "norm", "position", "head")
 
 
-def register_architecture(name: str, build_spec: Callable, *, replace: bool = False) -> None:
+def register_architecture(name: str, build_spec: Callable, read_config: Optional[Callable] = None, *,
+                          replace: bool = False) -> None:
+    """``read_config`` turns the raw JSON object of a folder's config.json into whatever ``build_spec`` takes
+    (default: the raw object itself)"""
     if name in _ARCHITECTURES and not replace:
         raise KeyError("architecture %r is already registered" % name)
-    _ARCHITECTURES[name] = Architecture(name, build_spec)
+    _ARCHITECTURES[name] = Architecture(name, build_spec, read_config or (lambda raw: raw))
 
 
 def architecture(name: str) -> Architecture:
@@ -40,6 +49,20 @@ def architecture(name: str) -> Architecture:
 def architectures() -> Tuple[str, ...]:
     _ensure_builtin()
     return tuple(sorted(_ARCHITECTURES))
+
+
+def model_from_config(raw: Mapping[str, Any]):
+    """(the architecture's typed configuration, its ModelSpec) for the JSON object of a config.json: the name is
+    looked up first, then the entry reads the keys it knows"""
+    arch = architecture(architecture_name(raw))
+    cfg = arch.read_config(raw)
+    spec = arch.build_spec(cfg)
+    spec.validate()
+    return cfg, spec
+
+
+def model_from_dir(model_dir: str):
+    return model_from_config(read_config_json(model_dir))
 
 
 def register_part(category: str, kind: str, cls: type, *, replace: bool = False) -> None:

@@ -52,17 +52,25 @@ class ScheduleEntry:
 
 @dataclass(frozen=True)
 class ModelSpec:
+    """``embedding`` and ``head`` are parts like the layers' (kinds of the categories "embedding" and "head"): what
+    turns token ids into the residual stream and the last hidden rows into logits is named by the architecture, with
+    its tensors' names and constants (a scale, a soft cap) as parameters. ``may_ignore``: patterns (``fnmatch``) of
+    tensor names a folder may hold that the model does not read. ``copies``: names a folder may hold only as a copy
+    of another tensor it holds (a tied head stored twice): ``{name: the tensor it must equal}``."""
+
     architecture: str
     vocab_size: int
     width: int
     layers: Tuple[LayerSpec, ...]
     schedule: Tuple[ScheduleEntry, ...]
     final_norm: PartSpec
-    embedding_name: str
     final_norm_prefix: str
-    head_name: Optional[str]            # None: the head is the embedding table (tied)
+    embedding: PartSpec
+    head: PartSpec
     stop_token_ids: Tuple[int, ...] = ()
-    max_positions: Optional[int] = None
+    max_positions: Optional[int] = None     # the most positions a sequence may reach (None: only the cache bounds it)
+    may_ignore: Tuple[str, ...] = ()
+    copies: Mapping[str, str] = field(default_factory=dict)
 
     @property
     def n_cache_entries(self) -> int:

@@ -536,14 +536,10 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
                        int* status, cudaStream_t st, AtRopeIn rp = AtRopeIn()) {
     auto kern = k_attn_mma<HD, DEC, ROPE>;
     const int sm = attn_smem_bytes<HD, DEC>();
-    static bool done = false;
-    if (!done) {
+    static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
+    if (kb_first_use(&once_tag)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
-        // two CTAs are meant to share an SM: ask for the largest shared-memory carve-out
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return (int)e;
-        done = true;
     }
     dim3 grid(grid_x, nkv, B);
     kb_launch(kern, grid, AT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, slot, q_start,

@@ -431,13 +431,10 @@ static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* 
     // tiles (Q and two stages of keys and values: 96 KB at head size 128) + barriers + what aligning the base to 1024
     // can cost when it is aligned to 128: two CTAs fit an SM
     const int sm = 128 * HD * 2 + FT_STAGES * 2 * 64 * HD * 2 + 256 + 768;
-    static bool done = false;
-    if (!done) {
+    static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
+    if (kb_first_use(&once_tag)) {
         cudaError_t e = cudaFuncSetAttribute(k_attn_tc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(k_attn_tc<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return (int)e;
-        done = true;
     }
     dim3 grid(nkv, grid_x, B);
     cudaError_t e = kb_launch(k_attn_tc<HD>, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot,

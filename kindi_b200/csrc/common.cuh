@@ -81,16 +81,26 @@ extern int g_kb_pdl;            // 1: launches carry the programmatic-serializat
 
 #ifdef __cplusplus
 #include <utility>
+#include <mutex>
+#include <unordered_set>
+// true the first time it is asked about this kernel on the current device, false ever after: function attributes
+// (the shared-memory opt-in, the carve-out) belong to a device, so they are set once per (device, kernel). Safe to
+// call from several host threads.
+static inline bool kb_first_use(const void* kern) {
+    static std::mutex mu;
+    static std::unordered_set<uint64_t> seen;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t key = ((uint64_t)(uintptr_t)kern << 8) ^ (uint64_t)(dev & 0xff);
+    std::lock_guard<std::mutex> g(mu);
+    return seen.insert(key).second;
+}
 // Every kernel of the library asks for the largest shared-memory partition of the SM, the one its tensor-core
 // kernels need: an SM re-partitions L1 and shared memory only when it is idle, so a step whose kernels all want the
 // same partition never waits for that, and a kernel launched early can become resident beside its predecessor.
 static inline void kb_same_partition(const void* kern) {
-    static const void* seen[64];
-    static int n_seen = 0;
-    for (int i = 0; i < n_seen; i++)
-        if (seen[i] == kern) return;
-    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
-    if (n_seen < 64) seen[n_seen++] = kern;
+    if (kb_first_use(kern))
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
 }
 template <typename... KArgs, typename... Args>
 static inline cudaError_t kb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,

@@ -402,11 +402,10 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, in
                        cudaStream_t st, int swiglu_ld, float* part, int* flags) {
     using S = GpSmem<BN, STAGES>;
     auto kern = k_gemm_pair<BN, STAGES, TC>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
+    if (kb_first_use(&once_tag)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
         if (e != cudaSuccess) return (int)e;
-        attr_done = true;
     }
     const int units = ((M + 2 * GP_BM - 1) / (2 * GP_BM)) * ((N + BN - 1) / BN);
     const int pairs = units < gp_sm_count() / 2 ? units : gp_sm_count() / 2;

@@ -311,11 +311,10 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
                      int splits, long long split_stride, int* status, cudaStream_t st, int swiglu_ld) {
     using S = TcSmem<BN, STAGES, MT, SWAP>;
     auto kern = k_gemm_tc<BN, STAGES, SWAP, TC, MT>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
+    if (kb_first_use(&once_tag)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
         if (e != cudaSuccess) return (int)e;
-        attr_done = true;
     }
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     int kbps = (total_kb + splits - 1) / splits;
@@ -532,11 +531,10 @@ static int launch_sk_swiglu(const CUtensorMap& mp, const CUtensorMap& mq, void* 
                             int ldh, float* part, int* flags, int* status, cudaStream_t st) {
     using S = TcSmem<BN, STAGES, 1, true>;
     auto kern = k_gemm_sk_swiglu<BN, STAGES>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
+    if (kb_first_use(&once_tag)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
         if (e != cudaSuccess) return (int)e;
-        attr_done = true;
     }
     const int tilesP = (rowsP + TC_BM - 1) / TC_BM;
     const int grid = tilesP < kb_sm_count() ? tilesP : kb_sm_count();

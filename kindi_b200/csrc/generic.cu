@@ -19,7 +19,7 @@ extern "C" void kb_set_pdl(int on) { g_kb_pdl = on ? 1 : 0; }
 // x[t][:] = table[tok[t]][:] as 32-bit (no scaling: kindi/nbq.cu:472-487)
 template <typename TW>
 __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ tok, float* __restrict__ x, int E,
-                        int vocab, int* status) {
+                        int vocab, float scale, int* status) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int t = blockIdx.x;
@@ -31,14 +31,40 @@ __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ to
         return;
     }
     const TW* row = table + (size_t)id * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) xr[i] = kb_to_f<TW>(row[i]);
+    if (scale == 1.0f) {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) xr[i] = kb_to_f<TW>(row[i]);
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) xr[i] = kb_to_f<TW>(row[i]) * scale;
+    }
 }
 
+// x[t] = table[tok[t]] * scale (scale 1: the row as stored, the reference's embedding: kindi/nbq.cu:472-487)
 extern "C" int kb_embed(const void* table, int wdtype, const int* tok, float* x, int T, int E, int vocab,
-                        int* status, cudaStream_t st) {
+                        float scale, int* status, cudaStream_t st) {
     if (T <= 0) return 0;
-    if (wdtype == KB_F32) kb_launch(k_embed<float>, T, 256, 0, st, (const float*)table, tok, x, E, vocab, status);
-    else kb_launch(k_embed<bf16>, T, 256, 0, st, (const bf16*)table, tok, x, E, vocab, status);
+    if (wdtype == KB_F32)
+        kb_launch(k_embed<float>, T, 256, 0, st, (const float*)table, tok, x, E, vocab, scale, status);
+    else kb_launch(k_embed<bf16>, T, 256, 0, st, (const bf16*)table, tok, x, E, vocab, scale, status);
+    KB_LAUNCH_RET();
+}
+
+// ------------------------------------------------------------------------------------------------ logits: scale, soft cap
+// z = z * scale, then (cap > 0) z = cap * tanh(z / cap), in place: the options a head part may carry
+__global__ void k_logit_post(float* __restrict__ z, long long n, float scale, float cap) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const float inv = cap > 0.0f ? 1.0f / cap : 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = z[i] * scale;
+        if (cap > 0.0f) v = cap * tanhf(v * inv);
+        z[i] = v;
+    }
+}
+
+extern "C" int kb_logit_post(float* z, long long n, float scale, float cap, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 1023) / 1024 < 1184 ? (n + 1023) / 1024 : 1184);
+    kb_launch(k_logit_post, blocks, 256, 0, st, z, n, scale, cap);
     KB_LAUNCH_RET();
 }
 

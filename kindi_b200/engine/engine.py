@@ -3,7 +3,11 @@
 ``step`` takes a batch of sequences, each with its next tokens (a whole prompt, or one token, or any run in
 between) and the places whose logits are wanted. It runs only those tokens, as one packed batch, against the cache
 that earlier steps left, stores their keys and values, and returns 32-bit logits at the wanted places. There is
-no padding, so no result can depend on it; a row's logits do not depend on what else is in the batch.
+no padding, so no result can depend on it. In float32 a row's logits do not depend on what else is in the batch or
+on how the tokens were cut into steps, bit for bit: every sum is taken in an order that depends on positions only.
+In bfloat16 they agree up to rounding: the serving kernels choose tile widths and the number of ways a product or a
+sequence's keys are split from the step's row count, so the last bits - and with them a greedy token at a near tie -
+can differ with the batch.
 
 The reference has three entry points for one sequence - ``step`` (one token, ``kindi/nanbeige.py:736-776``),
 ``prefill_batch`` (a prompt in chunks, head on the last row, ``:962-1021``) and ``check`` (up to 8 rows with logits
@@ -18,8 +22,7 @@ import torch
 
 from ..cache.pages import CacheFull
 from ..cache.sequence_cache import SequenceCache
-from ..config.model_config import ModelConfig
-from ..config.registry import architecture
+from ..config.registry import model_from_dir
 from ..config.spec import ModelSpec
 from ..kernels import lib as K
 from ..parts.base import StepContext
@@ -33,6 +36,10 @@ from ..config.runtime import GREEDY as _GREEDY      # noqa: E402
 
 class EngineError(RuntimeError):
     pass
+
+
+class OutOfDeviceMemory(EngineError):
+    """the weights, the cache and the working memory of the largest step do not fit the GPU's free memory"""
 
 
 class Engine:
@@ -53,30 +60,66 @@ class Engine:
         K.load()                                   # build / load the kernels now: fail loudly, not at first step
         self.dtype_name = dtype
         self.dtype = _DTYPES[dtype]
-        self.config: Optional[ModelConfig] = None
+        self.config = None                         # the architecture's typed configuration (None with ``spec=``)
         if spec is None:
             if model_dir is None:
                 raise EngineError("give a model folder, or a spec with tensors")
-            self.config = ModelConfig.from_dir(model_dir)
-            spec = architecture(self.config.architecture).build_spec(self.config)
+            # the folder's architecture name picks the registry entry, which reads its own config.json keys
+            self.config, spec = model_from_dir(model_dir)
         self.spec = spec
+        self.ctx = int(ctx)
+        self.max_batch = int(max_batch)
+        self.max_step_tokens = max(64, int(max_step_tokens))     # longer steps are run in pieces of this many tokens
+        self.plan = self._plan_memory(spec, tensors)
         if tensors is None:
-            tensors = load_tensors(model_dir, expected_tensors(spec), run_dtype=dtype, device=str(self.device))
+            tensors = load_tensors(model_dir, expected_tensors(spec), run_dtype=dtype, device=str(self.device),
+                                   may_ignore=spec.may_ignore, copies=spec.copies, log=self.log)
         else:
             tensors = {n: _to_run_dtype(t, dtype).to(self.device) for n, t in tensors.items()}
         self.model = DecoderModel(spec, tensors, dtype=self.dtype, device=self.device)
-        self.ctx = int(ctx)
-        self.max_batch = int(max_batch)
         self.cache = SequenceCache(cache_needs(spec), max_tokens=self.ctx, n_slots=self.max_batch,
                                    dtype=self.dtype, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
-        self.max_step_tokens = max(64, int(max_step_tokens))     # longer steps are run in pieces of this many tokens
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self.graph_replays = 0
         self._graph_warm = set()
+
+    def _plan_memory(self, spec: ModelSpec, tensors) -> Dict[str, int]:
+        """what the engine will hold on the device, counted before anything is allocated: the weights (twice the
+        fused ones while a part joins them), the cache, and the activations of the largest step; more than the GPU
+        has free is an error here, not an out-of-memory fault in the middle of loading. The reference plans its
+        memory before it loads in the same way (``kindi/nanbeige.py:316-397``)."""
+        el = 4 if self.dtype == torch.float32 else 2
+        shapes = expected_tensors(spec)
+        weights = 0
+        if tensors is None or any(not t.is_cuda for t in tensors.values()):
+            for n, shape in shapes.items():
+                k = 1
+                for d in shape:
+                    k *= d
+                weights += k * el
+        cache = SequenceCache.bytes_needed(cache_needs(spec), self.ctx, self.max_batch, self.dtype)
+        widest = max([spec.width] + [s[0] for s in shapes.values() if len(s) == 2 and s[0] != spec.vocab_size])
+        rows = min(self.max_step_tokens, self.ctx)
+        # residual + branch planes in 32-bit, the widest activation twice in the run dtype, logits of a decode batch
+        work = rows * (3 * spec.width * 4 + 2 * widest * max(el, 2)) + self.max_batch * spec.vocab_size * 4 * 2
+        plan = {"weights": weights, "cache": cache, "work": work, "total": weights + cache + work}
+        free, total = torch.cuda.mem_get_info(self.device)
+        plan["free"] = int(free)
+        gib = 2.0 ** 30
+        self.log("memory plan: weights %.2f GiB, cache %.2f GiB (ctx %d, %d slots), working memory of a %d-token step "
+                 "%.2f GiB; %.2f of %.2f GiB free on %s" % (weights / gib, cache / gib, self.ctx, self.max_batch, rows,
+                                                            work / gib, free / gib, total / gib, self.device))
+        if plan["total"] > free:
+            raise OutOfDeviceMemory(
+                "the model does not fit: weights %.2f GiB + cache %.2f GiB (ctx %d tokens, %d slots) + working memory "
+                "%.2f GiB = %.2f GiB, and %s has %.2f GiB free; lower ctx (the cache grows with it), max_batch or "
+                "max_step_tokens" % (weights / gib, cache / gib, self.ctx, self.max_batch, work / gib,
+                                     plan["total"] / gib, self.device, free / gib))
+        return plan
 
     # ------------------------------------------------------------------ slots
     def alloc(self) -> int:
@@ -101,6 +144,12 @@ class Engine:
             return self._step_in_pieces(entries, greedy)
         cache = self.cache
         before = [cache.length[e.slot] for e in entries]
+        limit = self.spec.max_positions
+        if limit is not None:
+            for e, n in zip(entries, before):
+                if n + len(e.tokens) > limit:
+                    raise EngineError("the sequence in slot %d would reach %d positions; the model's configuration "
+                                      "allows %d (max_position_embeddings)" % (e.slot, n + len(e.tokens), limit))
         ps = pack(entries, before)
         reserved = []
         try:
@@ -145,6 +194,11 @@ class Engine:
         """a step of more than max_step_tokens tokens: its pieces run one after another (activations stay bounded;
         a later piece reads the earlier ones from the cache) and the wanted rows are put back in the order of the
         entries and of their ``want`` lists"""
+        for e in entries:
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise ValueError("want place %d lies outside the sequence's %d tokens of this step"
+                                     % (w, len(e.tokens)))
         pieces = split_step(entries, self.max_step_tokens)
         got: Dict[Tuple[int, int], torch.Tensor] = {}            # (entry, place) -> logits row
         offset = [0] * len(entries)
@@ -330,6 +384,7 @@ class EngineStepper:
         from ..sampling.sampler import Sampler
         self.engine = engine
         self.ctx = engine.ctx
+        self.max_positions = engine.spec.max_positions          # the most positions one sequence may reach, or None
         self.max_batch = engine.max_batch
         self.sampler = Sampler(engine.device)
         self.seed = seed

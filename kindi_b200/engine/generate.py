@@ -83,14 +83,17 @@ def generate(stepper, prompts: Sequence[Sequence[int]], params: SamplingParams, 
              cancel: Optional[Callable[[], bool]] = None) -> GenerationResult:
     """generate for every prompt; returns the new tokens of each (without the stop token).
 
-    ``stepper`` offers ``ctx``, ``max_batch``, ``alloc()``, ``free(slot)`` and ``run(entries, params, seq_ids,
+    ``stepper`` offers ``ctx``, ``max_batch``, optionally ``max_positions``, ``alloc()``, ``free(slot)`` and ``run(entries, params, seq_ids,
     histories) -> [token per entry]`` (each entry wants exactly one place). ``on_tokens`` is called after each step
     with {request index: new token}; ``cancel()`` true ends all live sequences with finish "stop"
     (``kindi/nanbeige_gen.py:265-267``)."""
     stop = set(int(t) for t in stop_token_ids) | set(int(t) for t in params.stop_token_ids)
     n = len(prompts)
     prompts = [list(int(t) for t in p) for p in prompts]
-    max_new = [max_new_tokens(len(p), params.max_tokens, stepper.ctx) for p in prompts]
+    # one sequence can hold what the cache holds, and no more positions than the model's configuration allows
+    limit = getattr(stepper, "max_positions", None)
+    seq_ctx = stepper.ctx if limit is None else min(stepper.ctx, limit)
+    max_new = [max_new_tokens(len(p), params.max_tokens, seq_ctx) for p in prompts]
     batches = plan_batches([len(p) for p in prompts], max_new, stepper.ctx, stepper.max_batch)
     out: List[List[int]] = [[] for _ in range(n)]
     finish: List[str] = ["length"] * n

@@ -29,7 +29,8 @@ class KernelError(RuntimeError):
 
 
 _SIGS = {
-    "kb_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "kb_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "kb_logit_post": [c_void_p, c_longlong, c_float, c_float, c_void_p],
     "kb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p,
                        c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -149,13 +150,21 @@ def _need_cuda(*ts):
 
 
 # ----------------------------------------------------------------------------------------------- wrappers
-def embed(table: torch.Tensor, tok: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[t] (float32 [T, E]) = table[tok[t]]"""
+def embed(table: torch.Tensor, tok: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+          scale: float = 1.0) -> None:
+    """out[t] (float32 [T, E]) = table[tok[t]] * scale"""
     _need_cuda(table, tok, out)
     T, E = out.shape
     assert table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32 and tok.dtype == torch.int32
-    _check(load().kb_embed(_p(table), dt(table), _p(tok), _p(out), T, E, table.shape[0], _p(status), _stream()),
-           "embed")
+    _check(load().kb_embed(_p(table), dt(table), _p(tok), _p(out), T, E, table.shape[0], float(scale), _p(status),
+                           _stream()), "embed")
+
+
+def logit_post(logits: torch.Tensor, scale: float = 1.0, softcap: float = 0.0) -> None:
+    """logits (float32, contiguous) *= scale, then softcap * tanh(logits / softcap) when softcap > 0; in place"""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _check(load().kb_logit_post(_p(logits), logits.numel(), float(scale), float(softcap), _stream()), "logit_post")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float, out: torch.Tensor,

@@ -42,3 +42,32 @@ def rows_or_planes(ctx, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype
         if p is not None:
             return p
     return linear(ctx, a, w, out_dtype)
+
+
+# ----------------------------------------------------------------------------------------------- gate / up / SwiGLU
+GATE_UP_GROUP = 16      # rows of a gate group: a 32-column piece of a prompt-sized product's accumulator, the two
+                        # half-warps of an epilogue warp of a decode-sized one
+
+
+def join_gate_up(gate: torch.Tensor, up: torch.Tensor):
+    """(the joined ``[2F, K]`` matrix, its group size). Gate and up rows alternate in groups of ``GATE_UP_GROUP``: 16
+    gate rows, then the 16 up rows of the same outputs, so that a tile of the product holds both halves of its outputs
+    and SwiGLU is finished in the product's epilogue; the stand-alone SwiGLU kernel reads the same grouping. A size
+    that is no multiple of the group: all gates, then all ups (group = F)."""
+    f, width = gate.shape
+    group = GATE_UP_GROUP if f % GATE_UP_GROUP == 0 else f
+    n = f // group
+    joined = torch.stack([gate.view(n, group, width), up.view(n, group, width)], dim=1).reshape(2 * f, width)
+    return joined.contiguous(), group
+
+
+def gate_up_swiglu(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``silu(g) * u`` (``[M, F]`` in out_dtype) with ``[g | u] = y @ wgu^T``, ``wgu`` as ``join_gate_up`` made it:
+    inside the product where a tensor-core kernel takes the shape, else the product followed by the SwiGLU kernel"""
+    h = torch.empty((y.shape[0], f), dtype=out_dtype, device=y.device)
+    if ctx.fast and group == GATE_UP_GROUP and (fast.gemm_swiglu_decode(y, wgu, h, ctx.status)
+                                                or fast.gemm_swiglu_rows(y, wgu, h, ctx.status)):
+        return h
+    gu = rows_or_planes(ctx, y, wgu, out_dtype)
+    K.swiglu(gu, h, group)
+    return h

@@ -17,7 +17,7 @@ import torch
 
 from ..config.registry import part_class, register_part
 from ..config.spec import PartSpec
-from ..kernels import lib as K
+from ..kernels import attention as A
 from ..kernels import linear as L
 from .base import Branch, KVNeed, Mixer, StepContext, WeightView
 
@@ -49,8 +49,9 @@ class CausalSelfAttention(Mixer):
         self.scale = float(spec.get("scale") or 1.0 / math.sqrt(self.hd))
         pspec: PartSpec = spec["position"]
         self.position = part_class("position", pspec.kind)(pspec, width, weights, dtype=dtype, device=device)
-        if self.position.rotary_dim > self.hd:
-            raise ValueError("rotary_dim %d exceeds head_dim %d" % (self.position.rotary_dim, self.hd))
+        rot = self.position.rotation()
+        if rot is not None and rot[1] > self.hd:
+            raise ValueError("rotary_dim %d exceeds head_dim %d" % (rot[1], self.hd))
         ws = [weights("q_proj.weight"), weights("k_proj.weight"), weights("v_proj.weight")]
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v weights of %s are stored in different dtypes" % weights.prefix)
@@ -71,17 +72,14 @@ class CausalSelfAttention(Mixer):
             pool, table, n_pages = ctx.cache.kv_view(entry.cache)
             store_kv = nkv
         att = torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
-        if ctx.fast and ctx.decode and qkv.dim() == 3 and not reads_other:
-            # a decode step: the attention kernel sums, rotates and stores by itself where it takes the shape
-            from ..kernels import fast
-            if fast.attention_decode_rope(ctx, qkv, att, nh, nkv, hd, self.scale, self.window, self.position.inv_freq,
-                                          self.position.rotary_dim, pool, True, table, n_pages):
-                return Branch(L.planes(ctx, att, self.wo))
-        # 32-bit planes are summed, rotated and written out as rows; rows are rotated in place
+        if not reads_other and A.attention_from_planes(ctx, qkv, att, nh, nkv, hd, self.scale, self.window,
+                                                       self.position.rotation(), pool, table, n_pages):
+            # a small decode step of the serving kernels: the attention kernel summed the planes, rotated and stored
+            return Branch(L.planes(ctx, att, self.wo))
+        # the position encoding sums 32-bit planes, encodes and writes the queries out as rows (rows are encoded in
+        # place) and stores keys and values; then attention over the cache
         q = qkv if qkv.dim() == 2 else torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
-        K.rope_store(qkv, q, self.position.inv_freq, self.position.rotary_dim, ctx.pos, ctx.seq, ctx.slot, nh,
-                     store_kv, hd, pool if store_kv else None, table, n_pages, ctx.status)
-        from ..kernels import attention as A
+        self.position.encode_and_store(ctx, qkv, q, nh, store_kv, hd, pool, table, n_pages)
         A.attention(ctx, q, att, nh, nkv, hd, self.scale, self.window, pool, table, n_pages)
         return Branch(L.planes(ctx, att, self.wo))
 

@@ -109,6 +109,12 @@ class Part:
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
         return {}
 
+    @classmethod
+    def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
+        """how the random-weights mode draws the part's tensors that are not plain matrices: ``{suffix: "gain"}``
+        (around one: a norm's weight) or ``{suffix: "zero"}`` (a bias); every other tensor is drawn around zero"""
+        return {}
+
     def __init__(self, spec: PartSpec, width: int, weights: WeightView, *, dtype: torch.dtype, device):
         self.spec = spec
         self.width = width
@@ -130,8 +136,50 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """token ids to the 32-bit residual stream. Its tensors are named in full by its spec (no prefix)."""
+
+    category = "embedding"
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        """32-bit ``[T, width]`` rows of the step's tokens (``ctx.tok``)"""
+        raise NotImplementedError
+
+    def bytes_read(self, n_rows: int = 0) -> int:
+        return 0
+
+
+class Head(Part):
+    """normalised hidden rows to 32-bit logits. Its tensors are named in full by its spec (no prefix)."""
+
+    category = "head"
+
+    def forward(self, ctx: StepContext, y: torch.Tensor) -> torch.Tensor:
+        """``y`` (run dtype ``[R, width]``) -> float32 ``[R, vocab]``"""
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
+    """How a mixer's queries and keys learn their positions. The attention mixer hands its projections to
+    ``encode_and_store``: the encoding writes the encoded queries, and encodes and stores the keys (and stores the
+    values) at each row's position of its sequence's cache. An encoding that is a rotation of pairs also answers
+    ``rotation()`` so that kernels which rotate on the fly can take its table; any other encoding returns None there
+    and only ``encode_and_store`` is used."""
+
     category = "position"
+
+    def rotation(self):
+        """``(inv_freq float32 [rotary_dim / 2] on the device, rotary_dim)`` when the encoding is a rotation of the
+        pairs ``(i, i + rotary_dim / 2)`` by ``pos * inv_freq[i]``, else None"""
+        return None
+
+    def encode_and_store(self, ctx: StepContext, qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int,
+                         n_kv_store: int, head_dim: int, pool, table, n_pages: int) -> None:
+        """``qkv``: rows ``[T, (n_heads + 2 n_kv) head_dim]`` in the run dtype, or 32-bit planes ``[S, T, ...]`` whose
+        sum they are. Writes the encoded query heads to ``q_out`` (``[T, >= n_heads head_dim]``; may be ``qkv``
+        itself) and, when ``n_kv_store`` > 0, the encoded keys and the values of ``n_kv_store`` heads into ``pool``
+        at each row's position (``ctx.pos``) of its sequence's pages (``table``)"""
+        raise NotImplementedError
 
 
 class Mixer(Part):

@@ -35,6 +35,15 @@ class PreNormBlock(Block):
         return out
 
     @classmethod
+    def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
+        out = {}
+        for role, sub in cls._names(spec).items():
+            ps: PartSpec = spec[role]
+            for suffix, kind in part_class(_CATEGORY[role], ps.kind).tensor_init(ps, width).items():
+                out[sub + suffix] = kind
+        return out
+
+    @classmethod
     def cache_need(cls, spec: PartSpec, width: int):
         ps: PartSpec = spec["mixer"]
         return part_class("mixer", ps.kind).cache_need(ps, width)

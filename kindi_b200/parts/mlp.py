@@ -12,7 +12,6 @@ import torch
 
 from ..config.registry import register_part
 from ..config.spec import PartSpec
-from ..kernels import lib as K
 from ..kernels import linear as L
 from .base import Branch, FeedForward, StepContext, WeightView
 
@@ -29,25 +28,12 @@ class SwiGLU(FeedForward):
         g, u = weights("gate_proj.weight"), weights("up_proj.weight")
         if g.dtype != u.dtype:
             raise ValueError("gate and up weights of %s are stored in different dtypes" % weights.prefix)
-        # gate and up rows in groups of 16: 16 gate rows, then the 16 up rows of the same outputs. A tile of the
-        # product then holds both halves of its outputs (32 neighbouring accumulator columns of a prompt-sized product,
-        # the two half-warps of 32 accumulator lanes of a decode-sized one), so SwiGLU is finished in the product's
-        # epilogue; the stand-alone SwiGLU kernel reads the same grouping. (Sizes that are no multiple of 16: all
-        # gates, then all ups.)
-        self.group = 16 if self.f % 16 == 0 else self.f
-        n = self.f // self.group
-        self.wgu = torch.stack([g.view(n, self.group, width), u.view(n, self.group, width)], dim=1) \
-            .reshape(2 * self.f, width).contiguous()
+        # gate and up rows are put together in the order the products' SwiGLU epilogues want (the kernels' choice)
+        self.wgu, self.group = L.join_gate_up(g, u)
         self.wd = weights("down_proj.weight")
 
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:
-        from ..kernels import fast
-        h = torch.empty((y.shape[0], self.f), dtype=self.dtype, device=y.device)
-        fused = ctx.fast and self.group == 16 and (fast.gemm_swiglu_decode(y, self.wgu, h, ctx.status)
-                                                   or fast.gemm_swiglu_rows(y, self.wgu, h, ctx.status))
-        if not fused:
-            gu = L.rows_or_planes(ctx, y, self.wgu, self.dtype)
-            K.swiglu(gu, h, self.group)
+        h = L.gate_up_swiglu(ctx, y, self.wgu, self.group, self.f, self.dtype)
         return Branch(L.planes(ctx, h, self.wd))
 
     def bytes_read(self) -> int:

@@ -1,4 +1,5 @@
-"""A decoder built from a ``ModelSpec``: embedding, the layers' blocks run in schedule order, final norm, head.
+"""A decoder built from a ``ModelSpec``: its embedding part, the layers' blocks run in schedule order, the final norm
+and its head part.
 
 The head runs only on the rows whose logits are wanted (the reference runs its head on the last prompt row only,
 ``kindi/nanbeige.py:1011-1019``, and on every row of a check pass, ``:1126-1129``); logits are 32-bit.
@@ -11,23 +12,36 @@ import torch
 
 from ..config.registry import part_class
 from ..config.spec import ModelSpec
-from ..kernels import lib as K
-from ..kernels import linear as L
 from .base import Branch, StepContext, WeightView
 
 
-def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[int, ...]]:
-    """every tensor the model reads, by name, with its shape"""
-    out: Dict[str, Tuple[int, ...]] = {spec.embedding_name: (spec.vocab_size, spec.width)}
+def _model_parts(spec: ModelSpec):
+    """(category, part spec, tensor-name prefix) of every part that hangs directly on the model"""
+    yield "embedding", spec.embedding, ""
     for layer in spec.layers:
-        cls = part_class("block", layer.block.kind)
-        for suffix, shape in cls.tensor_shapes(layer.block, spec.width).items():
-            out[layer.prefix + suffix] = tuple(shape)
-    ncls = part_class("norm", spec.final_norm.kind)
-    for suffix, shape in ncls.tensor_shapes(spec.final_norm, spec.width).items():
-        out[spec.final_norm_prefix + suffix] = tuple(shape)
-    if spec.head_name is not None:
-        out[spec.head_name] = (spec.vocab_size, spec.width)
+        yield "block", layer.block, layer.prefix
+    yield "norm", spec.final_norm, spec.final_norm_prefix
+    yield "head", spec.head, ""
+
+
+def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[int, ...]]:
+    """every tensor the model reads, by name, with its shape (a tensor two parts name, a tied head's, once)"""
+    out: Dict[str, Tuple[int, ...]] = {}
+    for category, ps, prefix in _model_parts(spec):
+        for suffix, shape in part_class(category, ps.kind).tensor_shapes(ps, spec.width).items():
+            name, shape = prefix + suffix, tuple(int(n) for n in shape)
+            if out.setdefault(name, shape) != shape:
+                raise ValueError("tensor %s is asked for with shapes %s and %s" % (name, out[name], shape))
+    return out
+
+
+def tensor_inits(spec: ModelSpec) -> Dict[str, str]:
+    """the tensors that the random-weights mode does not draw around zero: name -> "gain" | "zero", as the parts
+    that own them say"""
+    out: Dict[str, str] = {}
+    for category, ps, prefix in _model_parts(spec):
+        for suffix, kind in part_class(category, ps.kind).tensor_init(ps, spec.width).items():
+            out[prefix + suffix] = kind
     return out
 
 
@@ -46,19 +60,20 @@ class DecoderModel:
         self.spec = spec
         self.dtype = dtype
         self.device = torch.device(device)
-        self.embedding = tensors[spec.embedding_name]
-        self.blocks = [part_class("block", l.block.kind)(l.block, spec.width, WeightView(tensors, l.prefix),
-                                                         dtype=dtype, device=device) for l in spec.layers]
-        self.final_norm = part_class("norm", spec.final_norm.kind)(
-            spec.final_norm, spec.width, WeightView(tensors, spec.final_norm_prefix), dtype=dtype, device=device)
-        self.head = self.embedding if spec.head_name is None else tensors[spec.head_name]
-        self.graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+
+        def make(category, ps, prefix):
+            return part_class(category, ps.kind)(ps, spec.width, WeightView(tensors, prefix), dtype=dtype,
+                                                 device=device)
+        self.embedding = make("embedding", spec.embedding, "")
+        self.blocks = [make("block", l.block, l.prefix) for l in spec.layers]
+        self.final_norm = make("norm", spec.final_norm, spec.final_norm_prefix)
+        self.head = make("head", spec.head, "")
+        self.graph_safe = all(p.graph_safe for p in [self.embedding, self.final_norm, self.head] + self.blocks)
 
     def forward(self, ctx: StepContext, rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """run the step's tokens through every scheduled layer (keys, values and state are stored on the way);
         returns 32-bit logits ``[len(rows), vocab]`` of the listed rows, or None when no row is wanted"""
-        x = torch.empty((ctx.T, self.spec.width), dtype=torch.float32, device=self.device)
-        K.embed(self.embedding, ctx.tok, x, ctx.status)
+        x = self.embedding.forward(ctx)
         pending: Optional[Branch] = None
         for entry in self.spec.schedule:
             ctx.entry = entry
@@ -67,12 +82,10 @@ class DecoderModel:
         if rows is None or rows.numel() == 0:
             return None
         y = self.final_norm.add_norm(ctx, x, pending, rows=rows)
-        return L.linear(ctx, y, self.head, torch.float32)
+        return self.head.forward(ctx, y)
 
     def bytes_read(self, n_rows: int) -> int:
         """weight bytes one step reads: every scheduled layer once, the head once, n_rows embedding rows"""
         per_layer = [b.bytes_read() for b in self.blocks]
         total = sum(per_layer[e.layer] for e in self.spec.schedule)
-        total += self.final_norm.bytes_read() + self.head.numel() * self.head.element_size()
-        total += n_rows * self.spec.width * self.embedding.element_size()
-        return total
+        return total + self.final_norm.bytes_read() + self.head.bytes_read() + self.embedding.bytes_read(n_rows)

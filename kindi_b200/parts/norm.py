@@ -22,6 +22,10 @@ class RMSNorm(Norm):
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
         return {"weight": (width,)}
 
+    @classmethod
+    def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
+        return {"weight": "gain"}
+
     def __init__(self, spec, width, weights: WeightView, *, dtype, device):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
         self.eps = float(spec["eps"])

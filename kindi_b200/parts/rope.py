@@ -1,5 +1,6 @@
-"""Position encodings. The attention mixer asks its position encoding for the rotation table it hands to the
-fused rotate-and-store kernel: ``inv_freq[i]`` for each rotated pair and the number of rotated dimensions.
+"""Position encodings. The attention mixer hands its projections to its position encoding, which rotates queries
+and keys and stores keys and values (one fused kernel); an encoding that is a rotation also offers its table
+(``inv_freq[i]`` for each rotated pair and the number of rotated dimensions) to kernels that rotate on the fly.
 
 Rotary (rotate-half pairing, for tensors in the safetensors layout): pair ``(i, i + rot/2)``, angle
 ``float(pos) * inv_freq[i]`` with ``inv_freq[i] = base ** (-2 i / rot)`` rounded to 32-bit; the reference's form
@@ -12,10 +13,23 @@ from __future__ import annotations
 import torch
 
 from ..config.registry import register_part
+from ..kernels import lib as K
 from .base import PositionEncoding
 
 
-class Rotary(PositionEncoding):
+class RotationEncoding(PositionEncoding):
+    """a rotation of the pairs (i, i + rotary_dim / 2) by pos * inv_freq[i]; subclasses set ``inv_freq`` (float32
+    ``[max(1, rotary_dim / 2)]`` on the device) and ``rotary_dim`` (even, at most the head size; 0 rotates nothing)"""
+
+    def rotation(self):
+        return self.inv_freq, self.rotary_dim
+
+    def encode_and_store(self, ctx, qkv, q_out, n_heads, n_kv_store, head_dim, pool, table, n_pages) -> None:
+        K.rope_store(qkv, q_out, self.inv_freq, self.rotary_dim, ctx.pos, ctx.seq, ctx.slot, n_heads, n_kv_store,
+                     head_dim, pool if n_kv_store else None, table, n_pages, ctx.status)
+
+
+class Rotary(RotationEncoding):
     def __init__(self, spec, width, weights, *, dtype, device):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
         self.base = float(spec["base"])
@@ -26,7 +40,7 @@ class Rotary(PositionEncoding):
         self.inv_freq = (self.base ** (-2.0 * i / self.rotary_dim)).to(torch.float32).to(device)
 
 
-class NoPosition(PositionEncoding):
+class NoPosition(RotationEncoding):
     def __init__(self, spec, width, weights, *, dtype, device):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
         self.rotary_dim = 0

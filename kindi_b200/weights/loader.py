@@ -11,6 +11,7 @@ float64 become 32-bit; integer tables become int32. With ``dtype="float32"`` eve
 """
 from __future__ import annotations
 
+import fnmatch
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
@@ -46,10 +47,14 @@ def target_dtype(stored: torch.dtype, run_dtype: str) -> torch.dtype:
 
 
 def load_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]], *, run_dtype: str = "bfloat16",
-                 device: str = "cpu", optional: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
+                 device: str = "cpu", may_ignore: Sequence[str] = (), copies: Optional[Mapping[str, str]] = None,
+                 log=None) -> Dict[str, torch.Tensor]:
     """read the tensors named in ``expected`` (name -> shape) from the folder's safetensors files.
 
-    ``optional`` names may be absent (a tied head). Raises one ``WeightError`` naming every problem."""
+    ``may_ignore``: ``fnmatch`` patterns of names the folder may hold that the model does not read. ``copies``:
+    ``{name: other}``: the folder may hold ``name`` only as a bit-for-bit copy of ``other`` (a tied head stored
+    beside the embedding table); a copy that differs is reported. Raises one ``WeightError`` naming every problem.
+    ``log`` is told about matrices that stay in 32-bit in a bfloat16 run."""
     try:
         paths = folder_files(model_dir)
     except (OSError, KeyError, ValueError) as e:
@@ -69,10 +74,16 @@ def load_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]], *, run
                 where[name] = f
     except (OSError, SafetensorsError) as e:
         raise WeightError(str(e))
-    opt = set(optional)
-    missing = sorted(n for n in expected if n not in where and n not in opt)
-    unexpected = sorted(n for n in where if n not in expected)
-    wrong_shape, wrong_dtype = [], []
+    copies = dict(copies or {})
+    missing = sorted(n for n in expected if n not in where)
+    unexpected = sorted(n for n in where if n not in expected and n not in copies
+                        and not any(fnmatch.fnmatchcase(n, pat) for pat in may_ignore))
+    wrong_shape, wrong_dtype, differs = [], [], []
+    for n, other in copies.items():
+        if n in where and other in where and n not in expected:
+            a, b = where[n].tensor(n), where[other].tensor(other)
+            if a.shape != b.shape or a.dtype != b.dtype or not torch.equal(a, b):
+                differs.append((n, other))
     for n, shape in expected.items():
         if n in where:
             dt, found = where[n].entries[n]
@@ -80,7 +91,7 @@ def load_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]], *, run
                 wrong_shape.append((n, tuple(shape), tuple(found)))
             if dt == "BOOL":
                 wrong_dtype.append((n, dt))
-    if missing or unexpected or wrong_shape or wrong_dtype or dup:
+    if missing or unexpected or wrong_shape or wrong_dtype or dup or differs:
         lines = ["the tensors in %s do not fit the model:" % model_dir]
         if missing:
             lines.append("  missing (%d): %s" % (len(missing), _some(missing)))
@@ -92,17 +103,26 @@ def load_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]], *, run
         if wrong_dtype:
             lines.append("  unusable dtype (%d): %s" % (len(wrong_dtype), _some(
                 ["%s is %s" % (n, d) for n, d in wrong_dtype])))
+        if differs:
+            lines.append("  stored beside the tensor it should equal, and different (%d): %s" % (len(differs), _some(
+                ["%s != %s" % (n, o) for n, o in differs])))
         if dup:
             lines.append("  stored in more than one file (%d): %s" % (len(dup), _some(sorted(dup))))
-        raise WeightError("\n".join(lines), missing, unexpected, [w[0] for w in wrong_shape],
-                          [w[0] for w in wrong_dtype])
+        raise WeightError("\n".join(lines), missing, unexpected + [n for n, _ in differs],
+                          [w[0] for w in wrong_shape], [w[0] for w in wrong_dtype])
     out: Dict[str, torch.Tensor] = {}
+    wide: List[str] = []
     for n in expected:
-        if n not in where:
-            continue
         t = where[n].tensor(n)
         td = target_dtype(t.dtype, run_dtype)
+        if run_dtype == "bfloat16" and td == torch.float32 and t.dim() >= 2:
+            wide.append(n)
         out[n] = t.to(device=device, dtype=td, copy=True).contiguous()
+    if wide and log is not None:
+        # a tensor stored in 32-bit stays 32-bit; its products then cannot use the bfloat16 tensor-core kernels
+        log("%d matrices of %s are stored in 32-bit and stay so (%s): their products run the general kernel with "
+            "32-bit weights, many times slower than the bfloat16 tensor-core kernels; store the folder in bfloat16 "
+            "for serving speed" % (len(wide), model_dir, _some(wide, 3)))
     for f in files:
         f.close()
     return out

@@ -5,9 +5,10 @@ import os
 import pytest
 
 import tiny
-from kindi_b200.config import (ConfigError, ModelConfig, SamplingParams, architecture, architectures, part_class,
-                               register_architecture, register_part)
+from kindi_b200.config import (ConfigError, SamplingParams, architecture, architectures, model_from_config,
+                               model_from_dir, part_class, register_architecture, register_part)
 from kindi_b200.config.spec import ScheduleEntry
+from kindi_b200.models.nanbeige import LlamaConfig as ModelConfig
 
 
 def test_reads_every_size_from_config():
@@ -50,10 +51,103 @@ def test_errors_name_the_key(change, word):
 
 def test_from_dir_errors(tmp_path):
     with pytest.raises(ConfigError):
-        ModelConfig.from_dir(str(tmp_path))
+        model_from_dir(str(tmp_path))
     (tmp_path / "config.json").write_text("{not json")
     with pytest.raises(ConfigError):
-        ModelConfig.from_dir(str(tmp_path))
+        model_from_dir(str(tmp_path))
+    (tmp_path / "config.json").write_text(json.dumps(tiny.TINY_C))
+    cfg, spec = model_from_dir(str(tmp_path))
+    assert cfg == ModelConfig.from_dict(tiny.TINY_C) and len(spec.layers) == 4
+
+
+def test_unknown_keys_are_an_error_and_harmless_ones_are_not():
+    """a key nothing reads is a model computed without it (the reference's rule for its own configuration,
+    kindi/config.py:86-88); keys that carry no arithmetic pass"""
+    ok = dict(tiny.TINY_A, transformers_version="4.55.0", use_cache=True, pad_token_id=0, initializer_range=0.02,
+              pretraining_tp=1, attention_dropout=0.0, _name_or_path="x", max_position_embeddings=4096,
+              rope_scaling=None, attention_bias=False, mlp_bias=False, hidden_act="silu", bos_token_id=1)
+    assert ModelConfig.from_dict(ok).max_position_embeddings == 4096
+    with pytest.raises(ConfigError) as e:
+        ModelConfig.from_dict(dict(tiny.TINY_A, frobnicate=3, other_thing=True))
+    assert "frobnicate" in str(e.value) and "other_thing" in str(e.value)
+    # keys of related architectures that change the arithmetic: refused by name unless they say "off"
+    for key, value in (("partial_rotary_factor", 0.5), ("attention_multiplier", 0.1), ("logits_scaling", 8.0),
+                       ("residual_multiplier", 0.2), ("embedding_multiplier", 12.0), ("final_logit_softcapping", 30.0),
+                       ("qk_norm", True), ("num_local_experts", 8), ("quantization_config", {"bits": 4}),
+                       ("mlp_bias", True)):
+        with pytest.raises(ConfigError) as e:
+            ModelConfig.from_dict(dict(tiny.TINY_A, **{key: value}))
+        assert key in str(e.value), key
+    assert ModelConfig.from_dict(dict(tiny.TINY_A, partial_rotary_factor=1.0, logits_scaling=1.0, qk_norm=False))
+    # a window that the folder says is not in use is not applied
+    assert ModelConfig.from_dict(dict(tiny.TINY_A, sliding_window=16, use_sliding_window=False)).sliding_window is None
+
+
+def test_another_architecture_reads_its_own_keys(tmp_path):
+    """a folder of an architecture with other keys - no attention heads at all, a GELU feed-forward - loads through
+    the registry: nothing of the Llama reader runs for it"""
+    from kindi_b200.config import ConfigReader, LayerSpec, ModelSpec, PartSpec, default_schedule
+    from kindi_b200.parts.model import expected_tensors, tensor_inits
+    from kindi_b200.weights import load_tensors
+    from kindi_b200.weights.random_init import write_random_model
+
+    def read(raw):
+        r = ConfigReader(raw)
+        r.ignore("architectures", "model_type")
+        if r.string("hidden_act") != "gelu":
+            raise ConfigError("config.json: the toy architecture is GELU only")
+        out = dict(width=r.integer("d_model"), layers=r.integer("n_layer"), vocab=r.integer("vocab_size"),
+                   inner=r.integer("d_inner"), eps=r.number("layer_norm_epsilon"), emb_scale=r.number("emb_scale", 1.0))
+        r.finish()
+        return out
+
+    def build(c):
+        norm = PartSpec("rmsnorm", {"eps": c["eps"]})
+        block = PartSpec("prenorm", {"norm1": norm, "mixer": PartSpec("toy_cfg_mixer", {}), "norm2": norm,
+                                     "feed_forward": PartSpec("toy_cfg_gelu", {"inner": c["inner"]})})
+        return ModelSpec(architecture="ToyGeluLM", vocab_size=c["vocab"], width=c["width"],
+                         layers=tuple(LayerSpec(block, "h.%d." % i) for i in range(c["layers"])),
+                         schedule=default_schedule(c["layers"]), final_norm=norm, final_norm_prefix="ln_f.",
+                         embedding=PartSpec("table", {"name": "wte", "vocab": c["vocab"], "scale": c["emb_scale"]}),
+                         head=PartSpec("linear", {"name": "head", "tied_to": "wte", "vocab": c["vocab"],
+                                                  "softcap": 30.0}))
+
+    from kindi_b200.parts.base import FeedForward, Mixer
+
+    class CfgMixer(Mixer):
+        @classmethod
+        def tensor_shapes(cls, spec, width):
+            return {"mix.weight": (width, width), "mix.bias": (width,)}
+
+        @classmethod
+        def tensor_init(cls, spec, width):
+            return {"mix.bias": "zero"}
+
+    class CfgGelu(FeedForward):
+        @classmethod
+        def tensor_shapes(cls, spec, width):
+            return {"fc.weight": (int(spec["inner"]), width), "proj.weight": (width, int(spec["inner"]))}
+
+    register_part("mixer", "toy_cfg_mixer", CfgMixer, replace=True)
+    register_part("feed_forward", "toy_cfg_gelu", CfgGelu, replace=True)
+    register_architecture("ToyGeluLM", build, read, replace=True)
+    raw = dict(architectures=["ToyGeluLM"], hidden_act="gelu", d_model=24, n_layer=2, vocab_size=50, d_inner=40,
+               layer_norm_epsilon=1e-5, emb_scale=3.0, use_cache=True)
+    cfg, spec = model_from_config(raw)
+    assert cfg["width"] == 24 and spec.embedding["scale"] == 3.0 and spec.head["softcap"] == 30.0
+    with pytest.raises(ConfigError) as e:
+        model_from_config(dict(raw, num_attention_heads=4))           # not a key of this architecture
+    assert "num_attention_heads" in str(e.value)
+    d = write_random_model(str(tmp_path / "toy"), raw, seed=1, dtype="float32")
+    shapes = expected_tensors(spec)
+    assert set(shapes) == {"wte", "ln_f.weight"} | {"h.%d.%s" % (i, s) for i in range(2) for s in (
+        "input_layernorm.weight", "self_attn.mix.weight", "self_attn.mix.bias", "post_attention_layernorm.weight",
+        "mlp.fc.weight", "mlp.proj.weight")}
+    assert tensor_inits(spec)["h.0.self_attn.mix.bias"] == "zero" and tensor_inits(spec)["ln_f.weight"] == "gain"
+    t = load_tensors(d, shapes, run_dtype="float32", may_ignore=spec.may_ignore, copies=spec.copies)
+    assert float(t["h.1.self_attn.mix.bias"].abs().sum()) == 0.0          # a bias is drawn as zero, not around one
+    assert abs(float(t["h.0.input_layernorm.weight"].mean()) - 1.0) < 0.05  # a gain around one
+    assert abs(float(t["h.0.self_attn.mix.weight"].mean())) < 0.01
 
 
 def test_layer_windows():
@@ -76,7 +170,9 @@ def test_registry_names_and_spec():
     assert mix[0]["n_heads"] == 6 and mix[0]["n_kv_heads"] == 2 and mix[0]["head_dim"] == 48
     assert spec.layers[0].block["norm1"]["eps"] == 3e-6
     assert ModelConfig.from_dict(tiny.TINY_B).tie_word_embeddings
-    assert architecture("llama").build_spec(ModelConfig.from_dict(tiny.TINY_B)).head_name is None
+    tied = architecture("llama").build_spec(ModelConfig.from_dict(tiny.TINY_B))
+    assert tied.head["tied_to"] == tied.embedding["name"] == "model.embed_tokens.weight"
+    assert model_from_config(tiny.TINY_A)[1].head["tied_to"] is None
     with pytest.raises(KeyError):
         part_class("mixer", "no_such_mixer")
     with pytest.raises(KeyError):

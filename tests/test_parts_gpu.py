@@ -176,7 +176,9 @@ def _toy_spec(width=64, vocab=97):
     # layer 0 runs twice (its second run owns cache entry 2); layer 2 reads the keys and values of the first run
     schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(2, 3, reads_cache_of=0))
     spec = ModelSpec(architecture="toy", vocab_size=vocab, width=width, layers=layers, schedule=schedule,
-                     final_norm=norm, embedding_name="emb", final_norm_prefix="fn.", head_name=None)
+                     final_norm=norm, final_norm_prefix="fn.",
+                     embedding=PartSpec("table", {"name": "emb", "vocab": vocab}),
+                     head=PartSpec("linear", {"name": "head", "tied_to": "emb", "vocab": vocab}))
     spec.validate()
     return spec
 
@@ -210,7 +212,7 @@ def _toy_plain(spec, w, tokens):
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 1.5e-2)])
 def test_toy_mixer_with_state_repeated_layer_and_shared_cache(tmp_path, dtype, tol):
     from kindi_b200.engine.engine import Engine
-    from kindi_b200.parts.model import cache_needs, expected_tensors
+    from kindi_b200.parts.model import cache_needs, expected_tensors, tensor_inits
     from kindi_b200.weights.random_init import random_tensors
     _toy_parts()
     spec = _toy_spec()
@@ -219,7 +221,7 @@ def test_toy_mixer_with_state_repeated_layer_and_shared_cache(tmp_path, dtype, t
     needs = cache_needs(spec)
     assert [type(n).__name__ for n in needs] == ["KVNeed", "StateNeed", "KVNeed", "NoneType"]
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
-    w = random_tensors(shapes, seed=9, std=0.05, dtype=tdt)
+    w = random_tensors(shapes, seed=9, std=0.05, dtype=tdt, inits=tensor_inits(spec))
     eng = Engine(spec=spec, tensors=w, ctx=1024, dtype=dtype, max_batch=3)
     assert not eng.cuda_graphs                                   # the toy mixer is not graph-safe
     reqs = tiny.random_requests(97, [40, 7, 90, 3, 66], seed=4)
@@ -242,7 +244,7 @@ def test_toy_mixer_with_state_repeated_layer_and_shared_cache(tmp_path, dtype, t
 # still recorded. The position encoding rotates the first half of each head with frequencies 0.3 / (i + 1).
 def _toy_routed_parts():
     from kindi_b200.config.registry import register_part
-    from kindi_b200.parts.base import Branch, FeedForward, PositionEncoding
+    from kindi_b200.parts import Branch, FeedForward, RotationEncoding
 
     class TopOneExperts(FeedForward):
         @classmethod
@@ -267,7 +269,7 @@ def _toy_routed_parts():
             h = torch.relu(torch.bmm(self.w1[pick], yf[:, :, None]))
             return Branch(torch.bmm(self.w2[pick], h)[None, :, :, 0].contiguous())
 
-    class HarmonicRotation(PositionEncoding):
+    class HarmonicRotation(RotationEncoding):
         def __init__(self, spec, width, weights, *, dtype, device):
             super().__init__(spec, width, weights, dtype=dtype, device=device)
             self.rotary_dim = int(spec["rotary_dim"])
@@ -289,8 +291,9 @@ def _toy_routed_spec(width=64, vocab=101):
     layers = (LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": att_h, "norm2": norm, "feed_forward": routed}), "a."),
               LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": att_r, "norm2": norm, "feed_forward": swiglu}), "b."))
     spec = ModelSpec(architecture="toy_routed", vocab_size=vocab, width=width, layers=layers,
-                     schedule=default_schedule(2), final_norm=norm, embedding_name="emb", final_norm_prefix="fn.",
-                     head_name="head")
+                     schedule=default_schedule(2), final_norm=norm, final_norm_prefix="fn.",
+                     embedding=PartSpec("table", {"name": "emb", "vocab": vocab}),
+                     head=PartSpec("linear", {"name": "head", "vocab": vocab}))
     spec.validate()
     return spec
 
@@ -329,14 +332,14 @@ def _toy_routed_plain(w, tokens, run_dtype):
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 1.5e-2)])
 def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype, tol):
     from kindi_b200.engine.engine import Engine
-    from kindi_b200.parts.model import expected_tensors
+    from kindi_b200.parts.model import expected_tensors, tensor_inits
     from kindi_b200.weights.random_init import random_tensors
     _toy_routed_parts()
     spec = _toy_routed_spec()
     shapes = expected_tensors(spec)
     assert shapes["a.mlp.router.weight"] == (3, 64) and shapes["a.mlp.experts.2.w2.weight"] == (64, 40)
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
-    w = random_tensors(shapes, seed=13, std=0.05, dtype=tdt)
+    w = random_tensors(shapes, seed=13, std=0.05, dtype=tdt, inits=tensor_inits(spec))
     # routing with wide margins, so that rounding cannot change an expert: token t carries a large value in feature
     # t % 3 and the router reads exactly these three features (all three experts are used by every request)
     w["emb"][:, :3] = 0

@@ -86,3 +86,31 @@ def test_sample_with_u_walks_token_order():
         assert P.sample_with_u(z, u, 1.0, 1.0, 0) == int(ids[order][np.searchsorted(c, u, side="right")])
     assert P.sample_with_u(z, 0.7, 0.0, 1.0, 0) == 1 and P.greedy(np.array([1.0, 3.0, 3.0])) == 1
     assert P.sample_with_u(z, 0.99, 1.0, 1.0, 1) == 1                                  # top_k 1 is greedy
+
+
+def test_needle_models_show_a_dropped_key_and_a_window_off_by_one(tmp_path):
+    """what makes the engine tests with a planted key able to fail: in the plain model itself, hiding the needle from
+    the last row only (a window of T - 1 positions hides position 0 from row T - 1 and nothing else), or moving a
+    layer's window by one position while the needle stands at its edge, changes that row's logits by several
+    times the bfloat16 tolerance of the engine tests (eight times and more for the hidden key, four for the window)"""
+    import random
+    import numpy as np
+    tol = 1.5e-2
+    for name in ("D", "E"):
+        cfg = tiny.TINY[name][0]
+        folder = tiny.make_needle_model(tmp_path, cfg, seed=31, dtype="float32", name="needle" + name)
+        m = P.load_model(folder)
+        full = dict(m, window=None, layer_types=None)
+        for seed, T in ((1, 100), (2, 400)):
+            toks = tiny.needle_request(cfg["vocab_size"], T, 0, T - 8, random.Random(seed))
+            whole = P.forward(full, toks).numpy()
+            cut = P.forward(dict(full, window=T - 1), toks).numpy()
+            assert np.array_equal(cut[:-1], whole[:-1])
+            assert np.abs(cut[-1] - whole[-1]).max() / np.abs(whole).max() > 8 * tol, (name, T)
+    cfg = tiny.TINY["E"][0]                                            # a window of 70 positions on its middle layer
+    m = P.load_model(tiny.make_needle_model(tmp_path, cfg, seed=31, dtype="float32", name="needleE"))
+    T = 120
+    toks = tiny.needle_request(cfg["vocab_size"], T, T - 1 - 69, T - 8, random.Random(3))   # the last row's window edge
+    a = P.forward(m, toks).numpy()
+    b = P.forward(dict(m, window=cfg["sliding_window"] - 1), toks).numpy()
+    assert np.abs(a[-1] - b[-1]).max() / np.abs(a).max() > 4 * tol       # (one layer of three has the window)

@@ -77,7 +77,7 @@ def test_folder_stored_in_the_other_dtype(models, tmp_path, stored, run):
     steps = tiny.trace_batched(reqs, batch=3, decode=8)
     eng = Engine(model_dir, ctx=tiny.max_live_tokens(steps), dtype=run, max_batch=3)
     want_dtype = torch.float32 if stored == "float32" or run == "float32" else torch.bfloat16
-    assert eng.model.embedding.dtype == want_dtype and eng.model.blocks[0].mixer.wqkv.dtype == want_dtype
+    assert eng.model.embedding.table.dtype == want_dtype and eng.model.blocks[0].mixer.wqkv.dtype == want_dtype
     out = str(tmp_path / "o")
     tiny.run_replay(eng, steps, out)
     got = tiny.collect(out, steps, 331)

@@ -7,15 +7,14 @@ import pytest
 import torch
 
 import tiny
-from kindi_b200.config import ModelConfig, architecture
+from kindi_b200.config import model_from_config
 from kindi_b200.parts.model import expected_tensors
 from kindi_b200.weights import SafetensorsFile, WeightError, load_tensors, write_file
 from kindi_b200.weights.random_init import write_random_model
 
 
 def _expected(name):
-    c = ModelConfig.from_dict(tiny.TINY[name][0])
-    return expected_tensors(architecture(c.architecture).build_spec(c))
+    return expected_tensors(model_from_config(tiny.TINY[name][0])[1])
 
 
 def test_random_folder_is_reproducible_and_readable_by_the_safetensors_package(tmp_path):
@@ -112,3 +111,41 @@ def test_sharded_folder(tmp_path):
         json.dump({"weight_map": {"a": "model-00001-of-00002.safetensors", "b": "model-00002-of-00002.safetensors"}}, f)
     got = load_tensors(d, {"a": (2, 2), "b": (3,)})
     assert got["a"].sum() == 4 and got["b"].numel() == 3
+
+
+def test_names_a_folder_may_hold_beside_what_the_model_reads(tmp_path):
+    """a tied model that also stores its head is accepted when the head is the embedding table bit for bit and refused
+    when it differs; rotary frequency buffers of older exports are ignored; anything else stays an error"""
+    from safetensors.torch import load_file
+    src = tiny.make_model(tmp_path / "src", "B")                       # B is tied
+    spec = model_from_config(tiny.TINY_B)[1]
+    t = load_file(src + "/model.safetensors")
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(16)
+    d = str(tmp_path / "with_head")
+    os.makedirs(d)
+    write_file(os.path.join(d, "model.safetensors"), t)
+    got = load_tensors(d, expected_tensors(spec), may_ignore=spec.may_ignore, copies=spec.copies)
+    assert set(got) == set(expected_tensors(spec))
+    with pytest.raises(WeightError):
+        load_tensors(d, expected_tensors(spec))                        # without the architecture's say-so: unexpected
+    t["lm_head.weight"][3, 5] += 1.0
+    t["model.layers.0.self_attn.something_else"] = torch.ones(2)
+    d2 = str(tmp_path / "other_head")
+    os.makedirs(d2)
+    write_file(os.path.join(d2, "model.safetensors"), t)
+    with pytest.raises(WeightError) as e:
+        load_tensors(d2, expected_tensors(spec), may_ignore=spec.may_ignore, copies=spec.copies)
+    assert "lm_head.weight != model.embed_tokens.weight" in str(e.value)
+    assert "something_else" in str(e.value) and "inv_freq" not in str(e.value)
+
+
+def test_wide_matrices_in_a_bfloat16_run_are_reported(tmp_path):
+    src = tiny.make_model(tmp_path / "src", "A", "float32")
+    said = []
+    got = load_tensors(src, _expected("A"), run_dtype="bfloat16", log=said.append)
+    assert got["model.layers.0.mlp.up_proj.weight"].dtype == torch.float32        # stored in 32-bit: stays so
+    assert len(said) == 1 and "32-bit" in said[0] and "slower" in said[0]
+    said.clear()
+    load_tensors(tiny.make_model(tmp_path / "src", "A", "bfloat16"), _expected("A"), run_dtype="bfloat16", log=said.append)
+    assert not said

@@ -145,3 +145,85 @@ def run_replay(engine, steps: List[dict], out_dir: str) -> None:
 def rel_err(a: np.ndarray, b: np.ndarray) -> float:
     """max |a - b| over max |b|"""
     return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64))) / (np.max(np.abs(b)) + 1e-30))
+
+
+# ------------------------------------------------------------------------------------------- a planted key
+NEEDLE, PROBE = 3, 4            # token ids: the needle's key stands out for every probe's query
+
+
+def make_needle_model(tmp_path, cfg: dict, seed: int, dtype: str = "bfloat16", strength: float = 14.0,
+                      name: str = "needle") -> str:
+    """a model folder with random weights N(0, 0.02) in which ONE key stands out: the score of a PROBE token's query
+    against a NEEDLE token's key is about `strength` above all others in the first layer (less in later layers),
+    wherever the two stand in the sequence, for the query heads of the first key/value head. With plain random weights
+    attention is nearly uniform, and a far key that a kernel drops, a window one position off or a page of another
+    sequence moves the logits by less than the bfloat16 tolerance; here a probe row's attention output IS the
+    needle's value, so any of these shows as an error many times the tolerance, while all other scores stay small
+    and rounding errors as usual.
+
+    How: the needle's embedding has one large feature (column 0), a probe's another (column 1); in every layer the
+    key projection of the first key/value head reads column 0 into its last rotated pair's first dimension and the
+    query projections of that group's heads read column 1 into the same dimension. That pair turns by less than a
+    thousandth of a radian over ten thousand positions (the smallest rotary frequency), so the score does not depend on
+    the distance."""
+    import torch
+    from kindi_b200.config.registry import model_from_config
+    from kindi_b200.parts.model import expected_tensors, tensor_inits
+    from kindi_b200.weights.random_init import random_tensors
+    from kindi_b200.weights.safetensors_io import write_file
+    d = os.path.join(str(tmp_path), "%s_%d_%s" % (name, seed, dtype))
+    if os.path.isfile(os.path.join(d, "model.safetensors")):
+        return d
+    os.makedirs(d, exist_ok=True)
+    _, spec = model_from_config(cfg)
+    tdt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
+    t = random_tensors(expected_tensors(spec), seed, dtype=torch.float32, inits=tensor_inits(spec))
+    width, hd = cfg["hidden_size"], cfg["head_dim"]
+    group = cfg["num_attention_heads"] // cfg["num_key_value_heads"]
+    w = (strength * hd ** 0.5 / width) ** 0.5          # q . k / sqrt(hd) = w^2 * width / sqrt(hd) = strength
+    emb = t["model.embed_tokens.weight"]
+    emb[:, 0:2] = 0.0
+    emb[NEEDLE, 0] = 1.0
+    emb[PROBE, 1] = 1.0
+    dim = hd // 2 - 1
+    for i in range(cfg["num_hidden_layers"]):
+        p = "model.layers.%d.self_attn." % i
+        t[p + "k_proj.weight"][dim, 0] = w
+        for h in range(group):
+            t[p + "q_proj.weight"][h * hd + dim, 1] = w
+    t = {n: v.to(tdt) for n, v in t.items()}
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(dict(cfg, torch_dtype=dtype), f)
+    write_file(os.path.join(d, "model.safetensors"), t, metadata={"format": "pt"})
+    return d
+
+
+def needle_request(vocab: int, length: int, needle_at: int, probes_from: int, rng: random.Random) -> List[int]:
+    """random tokens (neither needle nor probe) with the needle at `needle_at` and probes from `probes_from` on"""
+    toks = []
+    for i in range(length):
+        t = rng.randrange(vocab)
+        while t in (NEEDLE, PROBE):
+            t = rng.randrange(vocab)
+        toks.append(NEEDLE if i == needle_at else PROBE if i >= probes_from and i != needle_at else t)
+    return toks
+
+
+def trace_group(reqs: Dict[str, List[int]], decode: Dict[str, int], first_step: int = 0) -> List[dict]:
+    """one batch that starts together: request r brings all but its last decode[r] tokens in the first step (at least
+    one), then one token a step; a request ends with its last token, so the batch shrinks as it goes"""
+    first = {r: max(1, len(t) - decode[r]) for r, t in reqs.items()}
+    at = dict(first)
+    live = list(reqs)
+    ent = [{"id": r, "tokens": reqs[r][:first[r]], "want": list(range(first[r]))} for r in live]
+    steps, s = [], first_step
+    while True:
+        ended = [r for r in live if at[r] >= len(reqs[r])]
+        steps.append({"step": s, "entries": ent, "end": ended})
+        s += 1
+        live = [r for r in live if r not in ended]
+        if not live:
+            return steps
+        ent = [{"id": r, "tokens": [reqs[r][at[r]]], "want": [0]} for r in live]
+        for r in live:
+            at[r] += 1
