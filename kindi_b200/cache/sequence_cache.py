@@ -27,19 +27,24 @@ from .pages import PAGE, CacheError, CacheFull, FreeList, PageMap, pages_for
 class KVGroup:
     need: KVNeed
     entries: List[int]                 # cache entry indices, in pool order
-    pool: torch.Tensor                 # [len(entries), n_pages, 2, n_kv, PAGE, head_dim]
+    pool: torch.Tensor                 # [len(entries), pool pages, 2, n_kv, PAGE, head_dim]
     table: torch.Tensor                # int32 [n_slots, n_pages] on the device, -1 = not mapped
     pages: PageMap
+    n_pool_pages: int                  # pages of this group's pool (a window group needs fewer than a full one)
 
 
 class SequenceCache:
-    def __init__(self, needs: Sequence, *, max_tokens: int, n_slots: int, dtype: torch.dtype, device):
+    def __init__(self, needs: Sequence, *, max_tokens: int, n_slots: int, dtype: torch.dtype, device,
+                 max_step_tokens: Optional[int] = None):
         """``needs[i]`` is the KVNeed / StateNeed / None of cache entry i. ``max_tokens`` is the most tokens all
-        live sequences hold together, each sequence's count rounded up to a page."""
+        live sequences hold together, each sequence's count rounded up to a page. ``max_step_tokens``: the most new
+        tokens one step stores (None: unknown, as many as the cache holds); it bounds what a window group has to
+        keep, because pages behind the window are given back after every step."""
         self.device = torch.device(device)
         self.dtype = dtype
         self.n_pages = max(1, pages_for(max_tokens))
         self.n_slots = max(1, min(n_slots, self.n_pages))
+        self.max_step_tokens = max_step_tokens
         self.slots = FreeList(self.n_slots, "sequence slot")
         self.length: List[int] = [0] * self.n_slots
         self.groups: List[KVGroup] = []
@@ -56,24 +61,38 @@ class SequenceCache:
                 raise TypeError("cache entry %d asks for %r; a part's cache_need must be KVNeed, StateNeed or None"
                                 % (i, need))
         for need, entries in by_need.items():
-            pool = torch.zeros((len(entries), self.n_pages, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype,
+            n_pool = self.group_pages(need, self.n_pages, self.n_slots, max_step_tokens)
+            pool = torch.zeros((len(entries), n_pool, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype,
                                device=self.device)
             table = torch.full((self.n_slots, self.n_pages), -1, dtype=torch.int32, device=self.device)
-            g = KVGroup(need, entries, pool, table, PageMap(self.n_pages, self.n_slots, need.window))
+            g = KVGroup(need, entries, pool, table, PageMap(n_pool, self.n_slots, need.window), n_pool)
             for j, e in enumerate(entries):
                 self._where[e] = (len(self.groups), j)
             self.groups.append(g)
 
     # ------------------------------------------------------------------ sizes
     @staticmethod
-    def bytes_needed(needs: Sequence, max_tokens: int, n_slots: int, dtype: torch.dtype) -> int:
+    def group_pages(need: KVNeed, n_pages: int, n_slots: int, max_step_tokens: Optional[int]) -> int:
+        """pages of a group's pool. All keys: what the cache holds. A window: each sequence keeps the pages its window
+        touches (two more than the window fills: it starts and ends inside pages), and while a step runs also the
+        pages of its new tokens (each sequence's share again starts and ends inside pages); never more than a
+        full group"""
+        if need.window is None or max_step_tokens is None:
+            return n_pages
+        return min(n_pages, n_slots * (pages_for(need.window) + 4) + pages_for(max_step_tokens))
+
+    @staticmethod
+    def bytes_needed(needs: Sequence, max_tokens: int, n_slots: int, dtype: torch.dtype,
+                     max_step_tokens: Optional[int] = None) -> int:
         n_pages = max(1, pages_for(max_tokens))
+        n_slots = max(1, min(n_slots, n_pages))
         el = torch.empty((), dtype=dtype).element_size()
         total = 0
         seen = set()
         for need in needs:
             if isinstance(need, KVNeed):
-                total += n_pages * 2 * need.n_kv_heads * PAGE * need.head_dim * el
+                total += (SequenceCache.group_pages(need, n_pages, n_slots, max_step_tokens) * 2 * need.n_kv_heads
+                          * PAGE * need.head_dim * el)
                 if need not in seen:
                     seen.add(need)
                     total += min(n_slots, n_pages) * n_pages * 4
@@ -151,10 +170,10 @@ class SequenceCache:
 
     # ------------------------------------------------------------------ views for the parts
     def kv_view(self, entry: int):
-        """(pool of this entry [n_pages, 2, n_kv, PAGE, head_dim], page table, number of pages)"""
+        """(pool of this entry [pool pages, 2, n_kv, PAGE, head_dim], page table, number of pages of the pool)"""
         gi, j = self._where[entry]
         g = self.groups[gi]
-        return g.pool[j], g.table, self.n_pages
+        return g.pool[j], g.table, g.n_pool_pages
 
     def state_view(self, entry: int) -> torch.Tensor:
         return self.state[entry]

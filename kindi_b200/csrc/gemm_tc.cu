@@ -643,3 +643,26 @@ extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int
     }
 #undef TC_GO
 }
+
+// ------------------------------------------------------------------------------------------------ self-test of the bounded wait
+// One CTA waits on a barrier that nothing arrives at, with the given limit. The wait must give up after the limit, set
+// KB_ST_WAIT_TIMEOUT and return, so that the kernel ends by itself and the context stays usable: the behaviour every
+// kernel of the library relies on when an arrival is lost. out[0] = 1 when the wait reported a time-out (0: it claimed
+// the phase had completed), out[1] = nanoseconds spent in it.
+__global__ void k_wait_selftest(unsigned long long limit_ns, long long* out, int* status) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+        const uint64_t t0 = kb_globaltimer();
+        const bool ok = mbar_wait_ns(smem_u32(&bar), 0, status, limit_ns);
+        out[0] = ok ? 0 : 1;
+        out[1] = (long long)(kb_globaltimer() - t0);
+    }
+}
+
+extern "C" int kb_wait_selftest(unsigned long long limit_ns, long long* out, int* status, cudaStream_t st) {
+    if (limit_ns > 100000000ull) limit_ns = 100000000ull;           // a tenth of a second at most
+    k_wait_selftest<<<1, 32, 0, st>>>(limit_ns, out, status);
+    KB_LAUNCH_RET();
+}

@@ -50,18 +50,21 @@ __device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // wait for the phase with the given parity to complete; false (and the status bit) when the time runs out
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+__device__ __forceinline__ bool mbar_wait_ns(uint32_t bar, uint32_t parity, int* status, uint64_t limit_ns) {
     if (mbar_test(bar, parity)) return true;
     const uint64_t t0 = kb_globaltimer();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; i++)
             if (mbar_test(bar, parity)) return true;
-        if (kb_globaltimer() - t0 > KB_WAIT_NS) {
+        if (kb_globaltimer() - t0 > limit_ns) {
             atomicOr(status, KB_ST_WAIT_TIMEOUT);
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+    return mbar_wait_ns(bar, parity, status, KB_WAIT_NS);
 }
 
 // 2-D tile load: coordinates (x = innermost element index, y = row); x * element size must be a multiple of 16 bytes

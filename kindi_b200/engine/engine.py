@@ -78,7 +78,7 @@ class Engine:
             tensors = {n: _to_run_dtype(t, dtype).to(self.device) for n, t in tensors.items()}
         self.model = DecoderModel(spec, tensors, dtype=self.dtype, device=self.device)
         self.cache = SequenceCache(cache_needs(spec), max_tokens=self.ctx, n_slots=self.max_batch,
-                                   dtype=self.dtype, device=self.device)
+                                   dtype=self.dtype, device=self.device, max_step_tokens=self.max_step_tokens)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
@@ -101,7 +101,8 @@ class Engine:
                 for d in shape:
                     k *= d
                 weights += k * el
-        cache = SequenceCache.bytes_needed(cache_needs(spec), self.ctx, self.max_batch, self.dtype)
+        cache = SequenceCache.bytes_needed(cache_needs(spec), self.ctx, self.max_batch, self.dtype,
+                                           self.max_step_tokens)
         widest = max([spec.width] + [s[0] for s in shapes.values() if len(s) == 2 and s[0] != spec.vocab_size])
         rows = min(self.max_step_tokens, self.ctx)
         # residual + branch planes in 32-bit, the widest activation twice in the run dtype, logits of a decode batch

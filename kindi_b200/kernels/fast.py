@@ -228,8 +228,3 @@ def attention_decode_rope(ctx, qkv, out, nh, nkv, hd, scale, window, inv_freq, r
     K.attn_decode_rope(qkv, inv_freq, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool,
                        store, table, n_pages, grid_x=decode_splits(ctx, nkv), status=ctx.status)
     return True
-
-
-def gate_up_swiglu(y, ffn):
-    """the fused gate/up product with the SwiGLU epilogue, or None when it does not take this shape"""
-    return None

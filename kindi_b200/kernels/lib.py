@@ -58,6 +58,7 @@ _SIGS = {
     "kb_sample": [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
                   c_void_p],
     "kb_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_float, c_void_p],
+    "kb_wait_selftest": [ctypes.c_ulonglong, c_void_p, c_void_p, c_void_p],
 }
 
 
@@ -158,6 +159,17 @@ def embed(table: torch.Tensor, tok: torch.Tensor, out: torch.Tensor, status: tor
     assert table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32 and tok.dtype == torch.int32
     _check(load().kb_embed(_p(table), dt(table), _p(tok), _p(out), T, E, table.shape[0], float(scale), _p(status),
                            _stream()), "embed")
+
+
+def wait_selftest(status: torch.Tensor, limit_ns: int = 1_000_000):
+    """run the library's bounded wait on a barrier that nothing arrives at: it gives up after ``limit_ns`` (at most a
+    tenth of a second), sets ST_WAIT_TIMEOUT in ``status`` and the kernel ends. Returns (timed out, nanoseconds waited)
+    once the kernel has finished"""
+    _need_cuda(status)
+    out = torch.zeros(2, dtype=torch.int64, device=status.device)
+    _check(load().kb_wait_selftest(int(limit_ns), _p(out), _p(status), _stream()), "wait_selftest")
+    r = out.tolist()
+    return bool(r[0]), int(r[1])
 
 
 def logit_post(logits: torch.Tensor, scale: float = 1.0, softcap: float = 0.0) -> None:

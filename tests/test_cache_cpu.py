@@ -116,3 +116,36 @@ def test_cache_full_is_reported():
     with pytest.raises(CacheFull):
         c.reserve(a, PAGE + 1)
     c.check()
+
+
+def test_window_group_keeps_a_pool_of_the_window_plus_a_step():
+    """a group whose entries only ever read a window holds far fewer pages than a group that keeps every key, and
+    sequences can still grow to the cache's full length in steps of at most max_step_tokens new tokens"""
+    needs = [KVNeed(1, 16), KVNeed(1, 16, 100)]
+    c = SequenceCache(needs, max_tokens=40000, n_slots=2, dtype=torch.float32, device="cpu", max_step_tokens=256)
+    full, win = c.groups
+    assert full.n_pool_pages == 625 and win.n_pool_pages == 2 * (2 + 4) + 4
+    assert win.pool.shape[1] == win.n_pool_pages and c.kv_view(1)[2] == win.n_pool_pages
+    assert SequenceCache.bytes_needed(needs, 40000, 2, torch.float32, 256) < \
+        0.52 * SequenceCache.bytes_needed(needs, 40000, 2, torch.float32)
+    rng = random.Random(1)
+    a, b = c.alloc_slot(), c.alloc_slot()
+    la = lb = 0
+    while la + lb < 39000:
+        na = rng.choice((1, 1, 63, 64, 65, 128, 200))
+        nb = min(256 - na, rng.choice((1, 1, 56, 7)))
+        c.reserve(a, la + na)
+        c.reserve(b, lb + nb)
+        c.flush()
+        la, lb = la + na, lb + nb
+        c.commit(a, la)
+        c.commit(b, lb)
+        held = {p for p in c.groups[1].table[a].tolist() if p >= 0}
+        assert all(0 <= p < win.n_pool_pages for p in held)
+        rows_a = c.groups[1].pages.rows[a]       # the next query (position la) reads la - 99 .. la
+        assert (la - 1) // PAGE in rows_a and max(0, la - 99) // PAGE in rows_a
+    c.check()
+    c.free_slot(a)
+    c.free_slot(b)
+    c.check()
+    assert win.pages.pool.n_held == 0 and full.pages.pool.n_held == 0

@@ -205,3 +205,66 @@ def test_sampled_generation_walks_the_plain_model_and_sampler(tmp_path):
         assert len({tuple(t) for t in res.tokens}) > 1                 # sampling, not one fixed run
     eng.cache.check()
     assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_in_portions_of_any_size_sees_the_needle(tmp_path, dtype):
+    """a request brought in portions of 64, 2, 70, 1 and 33 tokens and then token by token (each portion reads the
+    earlier ones from the cache; the two-token and one-token portions are prompt-shaped and decode-shaped steps in the
+    middle of a prompt), in a slot and in pages that another request used before, with a window on one layer: every
+    row equals the whole-sequence plain model, and the probe rows rest on the needle near the start"""
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.engine.engine import Engine
+    cfg = tiny.TINY["E"][0]
+    folder = tiny.make_needle_model(tmp_path, cfg, seed=31, dtype=dtype, name="needleE")
+    vocab = cfg["vocab_size"]
+    rng = random.Random(5)
+    toks = tiny.needle_request(vocab, 190, 2, 120, rng)
+    other = tiny.needle_request(vocab, 150, 7, 100, rng)
+    want = P.forward(P.load_model(folder), toks).numpy()
+    eng = Engine(folder, ctx=256, dtype=dtype, max_batch=1)
+    slot = eng.alloc()
+    eng.step([StepEntry(slot, tuple(other), ())])                  # leaves its keys in the pages that come next
+    eng.free(slot)
+    slot = eng.alloc()
+    rows, at = [], 0
+    for n in (64, 2, 70, 1, 33) + (1,) * 20:
+        part = tuple(toks[at:at + n])
+        rows.append(eng.step([StepEntry(slot, part, tuple(range(n)))]).cpu().numpy())
+        at += n
+    eng.check_status()
+    assert at == 190
+    err = tiny.rel_err(np.concatenate(rows), want)
+    assert err <= TOL[dtype], err
+    eng.free(slot)
+    eng.cache.check()
+
+
+def test_window_layers_keep_a_small_pool_over_a_long_sequence(tmp_path):
+    """the layer with a window of 70 positions holds 14 pages while two sequences grow to 1,500 and 400 tokens (pages
+    behind the window are given back and used again many times); the layers that keep every key hold them all"""
+    from kindi_b200.engine.engine import Engine
+    cfg = tiny.TINY["E"][0]
+    folder = tiny.make_needle_model(tmp_path, cfg, seed=31, dtype="bfloat16", name="needleE")
+    vocab = cfg["vocab_size"]
+    rng = random.Random(11)
+    reqs = {"a": tiny.needle_request(vocab, 1500, 1500 - 20 - 62, 1500 - 20, rng),
+            "b": tiny.needle_request(vocab, 400, 4, 380, rng)}
+    m = P.load_model(folder)
+    want = {r: P.forward(m, t).numpy() for r, t in reqs.items()}
+    steps = tiny.trace_group(reqs, {"a": 20, "b": 20})
+    for e in steps[0]["entries"]:
+        e["want"] = [0, 69, 70, 71, 127, 128, len(e["tokens"]) - 1]
+    eng = Engine(folder, ctx=tiny.max_live_tokens(steps), dtype="bfloat16", max_batch=2, max_step_tokens=128)
+    win = [g for g in eng.cache.groups if g.need.window][0]
+    assert win.n_pool_pages == 2 * (2 + 4) + 2 and win.n_pool_pages < eng.cache.n_pages
+    out = str(tmp_path / "out")
+    tiny.run_replay(eng, steps, out)
+    eng.check_status()
+    got = tiny.collect(out, steps, vocab)
+    for r in reqs:
+        have = sorted(i for (rid, i) in got if rid == r)
+        assert len(have) == 27
+        err = tiny.rel_err(np.stack([got[(r, i)] for i in have]), want[r][have])
+        assert err <= TOL["bfloat16"], (r, err)
+    eng.cache.check()
