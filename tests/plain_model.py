@@ -4,11 +4,15 @@ Whole sequences, no cache, no batching, one function per part, float64 on the CP
 with the package: it reads config.json with ``json`` and the weights with the ``safetensors`` package, and every
 function restates a formula of the reference (cited as file:line of ahtx/kindi).
 
-The reference's own model code cannot be run here: its engine needs CuPy, a CUDA GPU and a quantised GGUF file
+The reference's model cannot be run here as a whole: its engine needs CuPy and a quantised GGUF file
 (``kindi/nanbeige.py:240``), and its kernels take only head size 128 and 5 or 7 query heads per key/value head
-(``kindi/nanbeige.py:260``). This file therefore rests on the formulas. The one piece of the reference that imports
-on the CPU, ``kindi/sampling.py`` (NumPy only), is compared with ``sampling_distribution`` below by
-``tests/golden/make_sampling_golden.py``; its outputs are stored under ``tests/golden/``.
+(``kindi/nanbeige.py:260``). What can be run is pinned on the reference's own output, stored under ``tests/golden/``
+with the scripts that made it: ``kindi/sampling.py`` (NumPy only) against ``sampling_distribution``
+(``make_sampling_golden.py``), and the reference's CUDA kernels that take and give 32-bit tensors - add + RMS norm,
+rotation with the key/value store, decode attention with its merge, prompt attention, argmax - compiled as they
+stand for sm_100a and run on a B200, against ``rms_norm``, ``rope_rotate_half``, ``attention`` and ``greedy``
+(``make_reference_kernel_golden.py``, ``tests/reference_kernels.py``). The matrix products, the SwiGLU and the order
+of a layer's operations rest on the formulas (the reference's own are int8 x low-bit products).
 """
 from __future__ import annotations
 
