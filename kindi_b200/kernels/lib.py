@@ -66,7 +66,7 @@ def load(verbose: bool = True):
     """build (when needed) and load the kernel library; raises when that is not possible"""
     global _lib
     if _lib is not None:
-        return _lib
+        return _lib if _timing is None else _timing
     path = _build.library_path(build=True, verbose=verbose)
     lib = ctypes.CDLL(path)
     for name, args in _SIGS.items():
@@ -81,6 +81,62 @@ def load(verbose: bool = True):
     lib._path = path
     _lib = lib
     return lib
+
+
+# ----------------------------------------------------------------------------------------------- per-kernel timing
+_timing = None
+
+# where an entry point's product sizes stand among its arguments (N, K), for the label of a timed launch
+_GEMM_NK = {"kb_gemm_tc": (5, 6), "kb_gemm_pair": (5, 6), "kb_gemm_simt": (7, 8), "kb_gemm_swiglu_decode": (4, 5)}
+
+
+class KernelTiming:
+    """``with KernelTiming() as t: engine.step(...)``: every launch of the library inside the block is bracketed by
+    CUDA events on the launching stream; ``t.summary()`` gives, per kind of launch (entry point, with the product's
+    sizes for matrix products), the number of launches and the device time in microseconds. Meant for steps that are
+    issued launch by launch (a recorded step is one launch to the host); the events themselves cost the device a
+    microsecond or two per launch, so compare shares."""
+
+    def __init__(self):
+        self.records = []
+
+    def __getattr__(self, name):                       # stands in for the library while timing is on
+        fn = getattr(_lib, name)
+        if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits"):
+            return fn
+
+        def timed(*args):
+            label = name[3:]
+            if name in _GEMM_NK:
+                n, k = _GEMM_NK[name]
+                label += " %dx%d" % ((2 * args[n], args[k]) if name == "kb_gemm_swiglu_decode" else (args[n], args[k]))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fn(*args)
+            e1.record()
+            self.records.append((label, e0, e1))
+            return rc
+        return timed
+
+    def __enter__(self):
+        global _timing
+        load()
+        _timing = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timing
+        _timing = None
+        return False
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for label, e0, e1 in self.records:
+            d = out.setdefault(label, {"launches": 0, "us": 0.0})
+            d["launches"] += 1
+            d["us"] += e0.elapsed_time(e1) * 1000.0
+        return {k: {"launches": v["launches"], "us": round(v["us"], 1)} for k, v in out.items()}
 
 
 def set_pdl(on: bool) -> None:
