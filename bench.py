@@ -7,8 +7,8 @@ The default run has the layer sizes of the benchmark's 3B-shaped configuration (
 4 key/value heads of size 128, feed-forward 10496, vocabulary 166144, bfloat16) with seeded random weights, a batch
 of 8 sequences each at a context of 8192 tokens. A "step" is one decode step of the whole batch. It prints ONE JSON
 line: ``value`` = decoded tokens a second timed on the device with CUDA events around exactly K steps; ``e2e`` = the
-same through the Python entry point the generation loop uses, with the step's tokens copied from pinned host memory
-and the picked tokens read back every step; ``prefill`` = one 2048-token prompt; ``roofline`` = the bytes a decode
+same through ``Engine.generate_batch`` (token ids in and out as Python lists; every step's inputs are copied from
+pinned host memory and its picked tokens read back); ``prefill`` = one 2048-token prompt; ``roofline`` = the bytes a decode
 step has to read (every weight once, the live sequences' keys and values) over its time, against the measured
 copy bandwidth; ``points`` = decoding at batch 1 and 64 (tokens a second); ``points_detail`` = the same and further
 batch sizes and context lengths, each with its step time, the bytes it has to read and its fraction of the copy
@@ -190,15 +190,10 @@ def fill_context(eng, batch: int, context: int):
 def bench_decode(eng, batch: int, context: int, steps: int, warmup: int, e2e: bool):
     """returns (device ms per step, e2e ms per step or None, launches in the device-timed region, bytes per step)"""
     import torch
-    from kindi_b200.config.runtime import SamplingParams
     from kindi_b200.engine.batch import StepEntry
-    from kindi_b200.engine.engine import EngineStepper
     from kindi_b200.kernels import lib as K
     slots = fill_context(eng, batch, context - 1)
-    greedy = SamplingParams(temperature=0.0, max_tokens=1)
-    stepper = EngineStepper(eng, 0)
     toks = [(17 * i + 5) % eng.spec.vocab_size for i in range(batch)]
-    seq_ids = list(range(batch))
 
     def one(toks):
         entries = [StepEntry(s, (t,), (0,)) for s, t in zip(slots, toks)]
@@ -219,134 +214,33 @@ def bench_decode(eng, batch: int, context: int, steps: int, warmup: int, e2e: bo
     launches = K.launch_count() - n0
     eng.check_status()
     e2e_ms = None
-    if e2e:
-        cur = toks
-        for _ in range(3):
-            cur = stepper.run([StepEntry(s, (t,), (0,)) for s, t in zip(slots, cur)], greedy, seq_ids, None)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            cur = stepper.run([StepEntry(s, (t,), (0,)) for s, t in zip(slots, cur)], greedy, seq_ids, None)
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1000.0 / steps
-    length = eng.length(slots[0])
     bytes_step = eng.weight_bytes_per_step(batch) + batch * context * eng.kv_bytes_per_token()
     for s in slots:
         eng.free(s)
+    if e2e:
+        e2e_ms = bench_e2e(eng, batch, context, steps)
     return dev_ms, e2e_ms, launches, bytes_step
 
 
-def kernel_times(eng, batch: int, context: int, prefill_tokens: int):
-    """device time per kind of launch: one decode step of `batch` sequences at `context` and one prompt pass, each
-    issued launch by launch (no recorded graph, launches strictly one after another) with CUDA events around every
-    launch. The events cost about a microsecond a launch and nothing overlaps, so the sums are larger than the
-    step times measured above: read them as shares."""
+def bench_e2e(eng, batch: int, context: int, steps: int, warm: int = 48) -> float:
+    """milliseconds per decode step through the call a user makes, ``Engine.generate_batch``: `batch` prompts of
+    context - 1 token ids given as Python lists, greedy tokens returned as Python lists. Every step copies its inputs
+    (positions, lengths, slots, row lists, tokens) from pinned host memory to the device and reads its picked tokens
+    and the status word back. The first `warm` decode steps are not timed (right after the prompt pass the GPU still
+    runs at the clocks its power limit forced during that pass: the first twenty to thirty steps take 3.2 ms instead
+    of 2.65 at batch 8); the time is the wall clock between the token callbacks of the last `steps` steps."""
     import random
-    from kindi_b200.engine.batch import StepEntry
-    from kindi_b200.kernels import lib as K
-    out = {}
-    graphs, eng.cuda_graphs = eng.cuda_graphs, False
-    K.set_pdl(False)
-    try:
-        slots = fill_context(eng, batch, context - 1)
-        entries = [StepEntry(s, ((17 * i + 5) % eng.spec.vocab_size,), (0,)) for i, s in enumerate(slots)]
-        eng.step(entries, greedy=True)
-        for s in slots:
-            eng.cache.commit(s, context - 1)
-        with K.KernelTiming() as t:
-            eng.step(entries, greedy=True)
-        out["decode_step_b%d_ctx%d" % (batch, context)] = t.summary()
-        for s in slots:
-            eng.free(s)
-        rng = random.Random(3)
-        ids = tuple(rng.randrange(eng.spec.vocab_size) for _ in range(prefill_tokens))
-        for timed in (False, True):
-            slot = eng.alloc()
-            if timed:
-                with K.KernelTiming() as t:
-                    eng.step([StepEntry(slot, ids, (prefill_tokens - 1,))])
-                out["prompt_pass_%d" % prefill_tokens] = t.summary()
-            else:
-                eng.step([StepEntry(slot, ids, (prefill_tokens - 1,))])
-            eng.free(slot)
-        eng.check_status()
-    finally:
-        eng.cuda_graphs = graphs
-        K.set_pdl(True)
-    return out
-
-
-REFERENCE_UNAVAILABLE = ("ahtx/kindi is not pip-installable offline (no setup.py or pyproject.toml); its Nanbeige engine "
-                         "needs CuPy (not installed, no index) and a quantised GGUF model file, has no bf16 "
-                         "safetensors path and serves one request at a time")
-
-
-def reference_kernel_times(cfg, context: int, prefill_tokens: int):
-    """the reference's own attention kernels (kindi/nbq.cu nbq_attn_part_g5 + nbq_attn_merge, kindi/nbq_fa.cu
-    nbq_fa_prefill_g5: fp16 cache, mma.sync) compiled as they stand for sm_100a and timed at this configuration's
-    shape: one decode query over `context` cached positions, and the attention of a `prefill_tokens` prompt. A
-    kernel-level bar on the same GPU, not an end-to-end number. None when the sources or a GPU are not at hand."""
-    import ctypes
-    import math
-    import tempfile
-    ref = os.path.join(ROOT, "baseline", "_ref", "kindi")
-    harness = os.path.join(ROOT, "tests", "golden", "reference_kernels_harness.cu")
-    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-    if not all(os.path.isfile(os.path.join(ref, f)) for f in ("nbq.cu", "nbq_fa.cu", "nbq_grids.h")) \
-            or not os.path.isfile(harness) or hd != 128 or nh != 5 * nkv:
-        return None
-    try:
-        import torch
-        if not torch.cuda.is_available():
-            return None
-        with tempfile.TemporaryDirectory() as tmp:
-            so = os.path.join(tmp, "libref.so")
-            r = subprocess.run(["nvcc", "-shared", "-Xcompiler", "-fPIC", "-std=c++14", "-use_fast_math", "-w", "-gencode",
-                                "arch=compute_100a,code=sm_100a", "-I", ref, harness, "-o", so], capture_output=True,
-                               text=True)
-            if r.returncode != 0:
-                return None
-            lib = ctypes.CDLL(so)
-            dev = "cuda"
-            ctx = (max(context, prefill_tokens) + 255) // 256 * 256
-            p = lambda t: ctypes.c_void_p(t.data_ptr())
-            kc = (torch.randn(nkv * ctx * hd, device=dev) * 0.5).to(torch.float16)
-            vc = (torch.randn(nkv * ctx * hd, device=dev) * 0.5).to(torch.float16)
-            scale = ctypes.c_float(1.0 / math.sqrt(hd))
-            nsplit = 16                                            # kindi/nanbeige.py:17
-            q = torch.randn(1, nh * hd, device=dev)
-            pos = torch.tensor([context - 1], dtype=torch.int32, device=dev)
-            part_o = torch.zeros(nh * nsplit * hd, device=dev)
-            part_ms = torch.zeros(nh * nsplit * 2, device=dev)
-            o = torch.empty(1, nh * hd, device=dev)
-            qp = torch.randn(prefill_tokens, nh * hd, device=dev)
-            op = torch.empty(prefill_tokens, nh * hd, device=dev)
-            flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # larger than the L2
-
-            def timed(fn, n=10):
-                best = []
-                for i in range(3 + n):
-                    flush.zero_()
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                    rc = fn()
-                    b.record()
-                    torch.cuda.synchronize()
-                    if rc != 0:
-                        raise RuntimeError("CUDA error %d" % rc)
-                    if i >= 3:
-                        best.append(a.elapsed_time(b) * 1000.0)
-                return round(statistics.median(best), 1)
-            dec = timed(lambda: lib.ref_attn_decode_g5(p(q), p(kc), p(vc), p(pos), ctx, scale, p(part_o), p(part_ms),
-                                                       nh * hd, nkv, nsplit, 1, p(o)))
-            pre = timed(lambda: lib.ref_fa_prefill_g5(p(qp), nh * hd, prefill_tokens, 0, p(kc), p(vc), ctx, scale, p(op),
-                                                      nkv))
-            return {"decode_attention_b1_ctx%d_us" % context: dec, "prefill_attention_%d_us" % prefill_tokens: pre,
-                    "what": "kindi/nbq.cu nbq_attn_part_g5 + nbq_attn_merge and kindi/nbq_fa.cu nbq_fa_prefill_g5, "
-                            "compiled unchanged for sm_100a, one layer, fp16 cache, L2 flushed before each launch, "
-                            "host-synchronised launches (a few microseconds of launch time are inside)"}
-    except Exception as e:                                          # noqa: BLE001
-        return {"error": str(e)[:200]}
+    import torch
+    rng = random.Random(5)
+    vocab = eng.spec.vocab_size
+    prompts = [[rng.randrange(vocab) for _ in range(context - 1)] for _ in range(batch)]
+    eng.generate_batch([p[:64] for p in prompts], temperature=0.0, max_tokens=8, stop_token_ids=())       # warm-up
+    torch.cuda.synchronize()
+    stamps = []
+    res = eng.generate_batch(prompts, temperature=0.0, max_tokens=warm + steps + 1, stop_token_ids=(),
+                             on_tokens=lambda d: stamps.append(time.perf_counter()))
+    assert all(len(t) == warm + steps + 1 for t in res.tokens) and len(stamps) == warm + steps + 1
+    return (stamps[-1] - stamps[-1 - steps]) * 1000.0 / steps
 
 
 def main(argv=None) -> int:
@@ -391,7 +285,7 @@ def main(argv=None) -> int:
         _K.set_pdl(False)
     point_batches = (1, 64) if a.preset == "3b" else (1,)          # 64 sequences of 8192 need too much cache beyond 3B
     max_b = max(a.batch, 1 if a.no_points else max(point_batches))
-    ctx = max_b * (a.context + a.steps * 2 + a.warmup + 256) + PREFILL_TOKENS + 64
+    ctx = max_b * (a.context + a.steps * 2 + a.warmup + 320) + PREFILL_TOKENS + 64
     if a.prefill_only:
         eng = build_engine(a.layers, a.prefill_tokens + 128, 2, base)
         pms = bench_prefill(eng, 2, max(1, min(a.steps, 3)), a.prefill_tokens)

@@ -80,6 +80,9 @@ class Engine:
         self.cache = SequenceCache(cache_needs(spec), max_tokens=self.ctx, n_slots=self.max_batch,
                                    dtype=self.dtype, device=self.device, max_step_tokens=self.max_step_tokens)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the tokens picked by the latest step, in the order of its wanted rows: a later step can take its tokens from
+        # here on the device, so the host need not have read them before it issues that step
+        self._picked = torch.zeros(max(self.max_batch, 1), dtype=torch.int32, device=self.device)
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
@@ -135,12 +138,19 @@ class Engine:
         return self.cache.length[slot]
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], greedy: bool = False):
+    def step(self, entries: Sequence[StepEntry], greedy: bool = False, tokens_from_previous: bool = False):
         """run the entries' tokens as one batch; returns float32 logits ``[number of wanted places, vocab]`` on the
         device (None when nothing is wanted). The cache then holds the tokens' keys and values. With ``greedy`` the
         return value is ``(logits, tokens)``, ``tokens`` being the argmax of each wanted row (int32, on the device;
         in the recorded decode step the pick is part of the recording). The tensors belong to the engine until its
-        next step."""
+        next step.
+
+        ``tokens_from_previous`` (a step of one token per sequence only): entry i's token is the one the previous
+        step picked for its i-th wanted row (``pick`` or ``greedy``), taken on the device; the entries' own token
+        values are ignored. The host can then issue this step before it has read the previous step's tokens (the
+        reference overlaps host and GPU the same way: ``step_begin`` / ``step_end``, ``kindi/nanbeige.py:741-776``)."""
+        if tokens_from_previous and (any(len(e.tokens) != 1 for e in entries) or len(entries) > self._picked.numel()):
+            raise ValueError("tokens_from_previous needs a step of one token per sequence")
         if sum(len(e.tokens) for e in entries) > self.max_step_tokens:
             return self._step_in_pieces(entries, greedy)
         cache = self.cache
@@ -172,11 +182,14 @@ class Engine:
             self._graph_warm.add(ps.B)
         picked = None
         if graph is not None:
-            logits = graph.replay(ps)
+            logits = graph.replay(ps, tokens_from_previous)
             picked = graph.picked
             self.graph_replays += 1
         else:
             ctx = self._context(ps)
+            if tokens_from_previous:
+                a, n = ps.off["tok"]
+                self._meta_dev[a:a + n].copy_(self._picked[:n])
             rows = None
             if ps.R:
                 a, n = ps.off["rows"]
@@ -187,9 +200,16 @@ class Engine:
         self.steps_run += 1
         if greedy:
             if picked is None and logits is not None:
-                picked = self._sampler().pick(logits, _GREEDY)
+                picked = self.pick(logits, _GREEDY)
             return logits, picked
         return logits
+
+    def pick(self, logits: torch.Tensor, params, uniforms=None, histories=None) -> torch.Tensor:
+        """the next token of each row of ``logits`` (the sampler's ``pick``), kept where a following step can take
+        its tokens from (``tokens_from_previous``)"""
+        R = logits.shape[0]
+        out = self._picked[:R] if R <= self._picked.numel() else None
+        return self._sampler().pick(logits, params, uniforms, histories, out=out)
 
     def _step_in_pieces(self, entries: Sequence[StepEntry], greedy: bool):
         """a step of more than max_step_tokens tokens: its pieces run one after another (activations stay bounded;
@@ -214,7 +234,7 @@ class Engine:
         order = [(i, w) for i, e in enumerate(entries) for w in e.want]
         logits = torch.stack([got[k] for k in order]) if order else None
         if greedy:
-            return logits, (self._sampler().pick(logits, _GREEDY) if logits is not None else None)
+            return logits, (self.pick(logits, _GREEDY) if logits is not None else None)
         return logits
 
     def _sampler(self):
@@ -260,20 +280,35 @@ class Engine:
                            max_kv=ps.max_kv, dtype=self.dtype, device=self.device, status=self.status,
                            cache=self.cache, fast=self.dtype == torch.bfloat16)
 
-    def read_picked(self, picked: torch.Tensor) -> List[int]:
-        """the picked tokens of a step on the host, together with the status check: both are copied into one pinned
-        buffer and the host waits for the device once"""
+    def begin_read(self, picked: torch.Tensor):
+        """start copying a step's picked tokens and the status word to the host (one pinned buffer, two copies, no
+        wait); ``end_read`` of the returned handle waits for them. Two reads may be under way at a time."""
         n = picked.numel()
-        buf = getattr(self, "_host_out", None)
-        if buf is None or buf.numel() < n + 1:
-            buf = self._host_out = torch.empty(max(n + 1, self.max_batch + 1), dtype=torch.int32, pin_memory=True)
+        ring = getattr(self, "_host_out", None)
+        if ring is None or ring[0].numel() < n + 1:
+            ring = self._host_out = [torch.empty(max(n + 1, self.max_batch + 1), dtype=torch.int32, pin_memory=True)
+                                     for _ in range(2)]
+            self._host_turn = 0
+        buf = ring[self._host_turn]
+        self._host_turn ^= 1
         buf[:n].copy_(picked.view(-1), non_blocking=True)
         buf[n:n + 1].copy_(self.status.view(-1), non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
+        done = torch.cuda.Event()
+        done.record()
+        return buf, n, done
+
+    def end_read(self, handle) -> List[int]:
+        buf, n, done = handle
+        done.synchronize()
         out = buf[:n + 1].tolist()
         if out[n]:
             self._raise_status(out[n])
         return out[:n]
+
+    def read_picked(self, picked: torch.Tensor) -> List[int]:
+        """the picked tokens of a step on the host, together with the status check: both are copied into one pinned
+        buffer and the host waits for the device once"""
+        return self.end_read(self.begin_read(picked))
 
     def check_status(self) -> None:
         """raise if a kernel of an earlier step met an index it had to skip (waits for the device)"""
@@ -358,14 +393,14 @@ class _DecodeGraph:
         try:
             with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
                 self.logits = engine.model.forward(ctx, rows)
-                self.picked = engine._sampler().pick(self.logits, _GREEDY)      # the greedy pick rides along
+                self.picked = engine.pick(self.logits, _GREEDY)                 # the greedy pick rides along
         finally:
             if was_on:
                 gc.enable()
         self.launches = K.launch_count() - n0        # recorded, not run
         K.add_launches(-self.launches)
 
-    def replay(self, ps: PackedStep) -> torch.Tensor:
+    def replay(self, ps: PackedStep, tokens_from_previous: bool = False) -> torch.Tensor:
         if self.copied is None:
             self.copied = torch.cuda.Event()
         else:
@@ -373,21 +408,23 @@ class _DecodeGraph:
         self.pin_np[:] = ps.meta
         self.meta.copy_(self.pin, non_blocking=True)
         self.copied.record()
+        if tokens_from_previous:
+            a, n = ps.off["tok"]
+            self.meta[a:a + n].copy_(self.engine._picked[:n])      # (before the recording's own pick overwrites them)
         self.graph.replay()
         K.add_launches(self.launches)
         return self.logits
 
 
 class EngineStepper:
-    """what the generation loop drives: the engine's step followed by the sampler, one host read per step"""
+    """what the generation loop drives: the engine's step followed by the sampler, one host read per step; ``launch``
+    and ``collect`` split a step so that the next one can be issued while this one runs"""
 
     def __init__(self, engine: Engine, seed: int):
-        from ..sampling.sampler import Sampler
         self.engine = engine
         self.ctx = engine.ctx
         self.max_positions = engine.spec.max_positions          # the most positions one sequence may reach, or None
         self.max_batch = engine.max_batch
-        self.sampler = Sampler(engine.device)
         self.seed = seed
         self._rng: Dict[int, object] = {}
 
@@ -397,12 +434,16 @@ class EngineStepper:
     def free(self, slot: int) -> None:
         self.engine.free(slot)
 
-    def run(self, entries, params, seq_ids, histories) -> List[int]:
+    def launch(self, entries, params, seq_ids, histories, tokens_from_previous: bool = False):
+        """issue a step and its pick and start reading the picked tokens; returns a handle for ``collect``. With
+        ``tokens_from_previous`` the entries' tokens are those the previous step picked, row for row, taken on the
+        device: the step can be issued before the previous one has been collected."""
         from ..sampling.sampler import SequenceRandom
+        eng = self.engine
         if params.greedy and (params.repeat_penalty == 1.0 or histories is None):
-            _, picked = self.engine.step(entries, greedy=True)
-            return self.engine.read_picked(picked)
-        logits = self.engine.step(entries)
+            _, picked = eng.step(entries, greedy=True, tokens_from_previous=tokens_from_previous)
+            return eng.begin_read(picked)
+        logits = eng.step(entries, tokens_from_previous=tokens_from_previous)
         uniforms = None
         if not params.greedy:
             uniforms = []
@@ -410,5 +451,12 @@ class EngineStepper:
                 if sid not in self._rng:
                     self._rng[sid] = SequenceRandom(self.seed, sid)
                 uniforms.append(self._rng[sid].next())
-        picked = self.sampler.pick(logits, params, uniforms, histories if params.repeat_penalty != 1.0 else None)
-        return self.engine.read_picked(picked)
+        picked = eng.pick(logits, params, uniforms, histories if params.repeat_penalty != 1.0 else None)
+        return eng.begin_read(picked)
+
+    def collect(self, handle) -> List[int]:
+        """the tokens of a launched step (waits for the device)"""
+        return self.engine.end_read(handle)
+
+    def run(self, entries, params, seq_ids, histories) -> List[int]:
+        return self.collect(self.launch(entries, params, seq_ids, histories))

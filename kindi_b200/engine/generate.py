@@ -8,8 +8,14 @@ min(max_tokens, ctx - len(prompt)))`` and a prompt of ``ctx`` tokens or more is 
 when the batch is empty the next one starts, in slots and pages that were used before. The reference serves one
 request at a time (``kindi/nanbeige_gen.py:261-283``); batches are this library's own.
 
-The loop's decisions need no GPU: it talks to a *stepper* (``alloc``, ``free``, ``run``), which is the engine in
-production and a stand-in in the CPU tests.
+Host and GPU overlap where the stepper allows it (``launch`` / ``collect``): while a step runs, the next one is
+issued with its tokens taken on the device from the running step's picks, and only then are the running step's
+tokens read (the reference's ``step_begin`` / ``step_end``, ``kindi/nanbeige.py:741-776``, used at
+``kindi/nanbeige_gen.py:343-347``). A sequence that turns out to have ended at a stop token has then run one step
+too many, whose result is dropped; the tokens of every sequence are the same as without the overlap.
+
+The loop's decisions need no GPU: it talks to a *stepper* (``alloc``, ``free``, ``run``; optionally ``launch`` and
+``collect``), which is the engine in production and a stand-in in the CPU tests.
 """
 from __future__ import annotations
 
@@ -98,20 +104,41 @@ def generate(stepper, prompts: Sequence[Sequence[int]], params: SamplingParams, 
     out: List[List[int]] = [[] for _ in range(n)]
     finish: List[str] = ["length"] * n
     stats = GenerationStats(prompt_tokens=sum(len(p) for p in prompts), batches=len(batches))
+    # issuing the next step before this step's tokens are read needs a stepper that splits a step, and a pick that
+    # needs no tokens on the host (the repeat penalty reads the sequence's history)
+    overlap = hasattr(stepper, "launch") and hasattr(stepper, "collect") and params.repeat_penalty == 1.0
     for batch in batches:
         slots = {i: stepper.alloc() for i in batch}
-        live = list(batch)
+        rows = list(batch)                       # the sequences of the step in flight, in the order of its rows
         try:
             t0 = time.perf_counter()
-            entries = [StepEntry(slots[i], tuple(prompts[i]), (len(prompts[i]) - 1,)) for i in live]
-            toks = stepper.run(entries, params, live, [prompts[i] for i in live])
-            stats.prompt_s += time.perf_counter() - t0
-            stats.steps += 1
-            t0 = time.perf_counter()
+            entries = [StepEntry(slots[i], tuple(prompts[i]), (len(prompts[i]) - 1,)) for i in rows]
+            handle = stepper.launch(entries, params, rows, None) if overlap else None
+            first = True
             while True:
+                ahead = None
+                if overlap and all(i in slots and len(out[i]) + 1 < max_new[i] for i in rows):
+                    # every row is alive and nobody leaves after this step for its length: the next step has the same
+                    # rows, so it can run on the tokens this step leaves on the device (a stop token shows only when
+                    # they have been read)
+                    nxt_entries = [StepEntry(slots[i], (0,), (0,)) for i in rows]
+                    ahead = stepper.launch(nxt_entries, params, rows, None, tokens_from_previous=True)
+                    stats.steps += 1
+                if overlap:
+                    toks = stepper.collect(handle)
+                else:
+                    hist = [prompts[i] if first else prompts[i] + out[i] for i in rows]
+                    toks = stepper.run(entries, params, rows, hist)
+                if first:
+                    stats.prompt_s += time.perf_counter() - t0
+                    stats.steps += 1
+                    t0 = time.perf_counter()
+                    first = False
                 nxt: List[int] = []
                 emitted: Dict[int, int] = {}
-                for i, t in zip(live, toks):
+                for i, t in zip(rows, toks):
+                    if i not in slots:
+                        continue                 # ended earlier; this row of a step issued ahead is dropped
                     t = int(t)
                     if t in stop:
                         finish[i] = "stop"
@@ -129,12 +156,22 @@ def generate(stepper, prompts: Sequence[Sequence[int]], params: SamplingParams, 
                 if cancel is not None and nxt and cancel():
                     for i in nxt:
                         finish[i] = "stop"
+                        stepper.free(slots.pop(i))
                     nxt = []
-                live = nxt
-                if not live:
+                if ahead is not None:
+                    # the step issued ahead is in flight with the old rows; rows that have ended meanwhile are dropped
+                    # when it is collected
+                    handle = ahead
+                    if not nxt:
+                        stepper.collect(handle)
+                        break
+                    continue
+                if not nxt:
                     break
-                entries = [StepEntry(slots[i], (out[i][-1],), (0,)) for i in live]
-                toks = stepper.run(entries, params, live, [prompts[i] + out[i] for i in live])
+                rows = nxt
+                entries = [StepEntry(slots[i], (out[i][-1],), (0,)) for i in rows]
+                if overlap:
+                    handle = stepper.launch(entries, params, rows, None)
                 stats.steps += 1
             stats.gen_s += time.perf_counter() - t0
         finally:

@@ -44,13 +44,15 @@ class Sampler:
         self.device = torch.device(device)
 
     def pick(self, logits: torch.Tensor, params: SamplingParams, uniforms: Optional[Sequence[float]] = None,
-             histories: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+             histories: Optional[Sequence[Sequence[int]]] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """logits: float32 [R, V] on the device (changed in place by the repeat penalty). Returns int32 [R] on the
-        device. ``uniforms``: one number in [0, 1) per row (needed unless greedy). ``histories``: each row's tokens
-        so far, for the repeat penalty."""
+        device (``out`` when given). ``uniforms``: one number in [0, 1) per row (needed unless greedy).
+        ``histories``: each row's tokens so far, for the repeat penalty."""
         R, V = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1
-        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        if out is None:
+            out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        assert out.dtype == torch.int32 and out.numel() == R and out.is_contiguous()
         lib = K.load()
         st = torch.cuda.current_stream().cuda_stream
         if params.repeat_penalty != 1.0 and histories is not None:

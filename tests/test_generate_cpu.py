@@ -153,3 +153,74 @@ def test_split_step_keeps_every_token_and_place():
         for i, e in enumerate(entries):
             assert tuple(seen[i]) == e.tokens and tuple(places[i]) == e.want
     assert len(split_step(entries, 64)) == 1
+
+
+class OverlapStepper(FakeStepper):
+    """a stepper that splits a step: ``launch`` computes at once what the device would (its picks are kept "on the
+    device" for a following step that asks for them) and ``collect`` hands the tokens over; it checks that no step is
+    ever issued on tokens of the host that the host has not collected yet, and that at most two steps are under way"""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.last_picks = None
+        self.in_flight = 0
+        self.ahead = 0
+
+    def launch(self, entries, params, seq_ids, histories, tokens_from_previous=False):
+        assert histories is None and self.in_flight <= 1
+        assert len({e.slot for e in entries}) == len(entries) and all(e.slot in self.held for e in entries)
+        if tokens_from_previous:
+            assert self.last_picks is not None and len(self.last_picks) == len(entries)
+            assert all(len(e.tokens) == 1 for e in entries)
+            toks = [(t,) for t in self.last_picks]
+            self.ahead += 1
+        else:
+            assert self.in_flight == 0               # tokens from the host: everything before has been collected
+            toks = [e.tokens for e in entries]
+        self.steps.append([(e.slot, len(t)) for e, t in zip(entries, toks)])
+        out = []
+        for e, t in zip(entries, toks):
+            self.sums[e.slot] += sum(t)
+            out.append(self.sums[e.slot] % 97)
+        self.last_picks = out
+        self.in_flight += 1
+        return list(out)
+
+    def collect(self, handle):
+        self.in_flight -= 1
+        return handle
+
+
+@pytest.mark.parametrize("max_tokens,stops", [(12, (31, 4)), (3, ()), (1, ()), (40, (5, 11, 60, 77))])
+def test_overlapped_loop_gives_the_same_tokens(max_tokens, stops):
+    prompts = [[1, 2, 3], [50], [7] * 20, [9, 9], [13, 1], [2] * 9]
+    p = SamplingParams(temperature=0.0, max_tokens=max_tokens, stop_token_ids=stops)
+    plain = generate(FakeStepper(max_batch=4, n_slots=4), prompts, p)
+    st = OverlapStepper(max_batch=4, n_slots=4)
+    seen = []
+    res = generate(st, prompts, p, on_tokens=lambda d: seen.append(dict(d)))
+    assert res.tokens == plain.tokens and res.finish == plain.finish
+    for i, pr in enumerate(prompts):
+        assert res.tokens[i] == _expect(pr, max_tokens, stop=stops)[0]
+    assert not st.held and st.in_flight == 0
+    assert sum(len(d) for d in seen) == sum(len(t) for t in res.tokens)
+    if max_tokens > 3:
+        assert st.ahead > 0                          # steps were issued ahead of the read
+
+
+def test_overlap_is_off_when_the_pick_needs_the_history():
+    st = OverlapStepper()
+    p = SamplingParams(temperature=0.0, max_tokens=4, repeat_penalty=1.2)
+    res = generate(st, [[1, 2, 3]], p)
+    assert st.ahead == 0 and res.tokens[0] == _expect([1, 2, 3], 4)[0]
+
+
+def test_cancel_with_a_step_under_way():
+    st = OverlapStepper()
+    calls = []
+
+    def cancel():
+        calls.append(1)
+        return len(calls) >= 3
+    res = generate(st, [[1, 2, 3], [4]], SamplingParams(temperature=0.0, max_tokens=50), cancel=cancel)
+    assert res.finish == ["stop", "stop"] and len(res.tokens[0]) == 3 and not st.held and st.in_flight == 0
