@@ -243,6 +243,119 @@ def bench_e2e(eng, batch: int, context: int, steps: int, warm: int = 48) -> floa
     return (stamps[-1] - stamps[-1 - steps]) * 1000.0 / steps
 
 
+def kernel_times(eng, batch: int, context: int, prefill_tokens: int):
+    """device time per kind of launch: one decode step of `batch` sequences at `context` and one prompt pass, each
+    issued launch by launch (no recorded graph, launches strictly one after another) with CUDA events around every
+    launch. The events cost about a microsecond a launch and nothing overlaps, so the sums are larger than the
+    step times measured above: read them as shares."""
+    import random
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.kernels import lib as K
+    out = {}
+    graphs, eng.cuda_graphs = eng.cuda_graphs, False
+    K.set_pdl(False)
+    try:
+        slots = fill_context(eng, batch, context - 1)
+        entries = [StepEntry(s, ((17 * i + 5) % eng.spec.vocab_size,), (0,)) for i, s in enumerate(slots)]
+        eng.step(entries, greedy=True)
+        for s in slots:
+            eng.cache.commit(s, context - 1)
+        with K.KernelTiming() as t:
+            eng.step(entries, greedy=True)
+        out["decode_step_b%d_ctx%d" % (batch, context)] = t.summary()
+        for s in slots:
+            eng.free(s)
+        rng = random.Random(3)
+        ids = tuple(rng.randrange(eng.spec.vocab_size) for _ in range(prefill_tokens))
+        for timed in (False, True):
+            slot = eng.alloc()
+            if timed:
+                with K.KernelTiming() as t:
+                    eng.step([StepEntry(slot, ids, (prefill_tokens - 1,))])
+                out["prompt_pass_%d" % prefill_tokens] = t.summary()
+            else:
+                eng.step([StepEntry(slot, ids, (prefill_tokens - 1,))])
+            eng.free(slot)
+        eng.check_status()
+    finally:
+        eng.cuda_graphs = graphs
+        K.set_pdl(True)
+    return out
+
+
+REFERENCE_UNAVAILABLE = ("ahtx/kindi is not pip-installable offline (no setup.py or pyproject.toml); its Nanbeige engine "
+                         "needs CuPy (not installed, no index) and a quantised GGUF model file, has no bf16 "
+                         "safetensors path and serves one request at a time")
+
+
+def reference_kernel_times(cfg, context: int, prefill_tokens: int):
+    """the reference's own attention kernels (kindi/nbq.cu nbq_attn_part_g5 + nbq_attn_merge, kindi/nbq_fa.cu
+    nbq_fa_prefill_g5: fp16 cache, mma.sync) compiled as they stand for sm_100a and timed at this configuration's
+    shape: one decode query over `context` cached positions, and the attention of a `prefill_tokens` prompt. A
+    kernel-level bar on the same GPU, not an end-to-end number. None when the sources or a GPU are not at hand."""
+    import ctypes
+    import math
+    import tempfile
+    ref = os.path.join(ROOT, "baseline", "_ref", "kindi")
+    harness = os.path.join(ROOT, "tests", "golden", "reference_kernels_harness.cu")
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    if not all(os.path.isfile(os.path.join(ref, f)) for f in ("nbq.cu", "nbq_fa.cu", "nbq_grids.h")) \
+            or not os.path.isfile(harness) or hd != 128 or nh != 5 * nkv:
+        return None
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        with tempfile.TemporaryDirectory() as tmp:
+            so = os.path.join(tmp, "libref.so")
+            r = subprocess.run(["nvcc", "-shared", "-Xcompiler", "-fPIC", "-std=c++14", "-use_fast_math", "-w", "-gencode",
+                                "arch=compute_100a,code=sm_100a", "-I", ref, harness, "-o", so], capture_output=True,
+                               text=True)
+            if r.returncode != 0:
+                return None
+            lib = ctypes.CDLL(so)
+            dev = "cuda"
+            ctx = (max(context, prefill_tokens) + 255) // 256 * 256
+            p = lambda t: ctypes.c_void_p(t.data_ptr())
+            kc = (torch.randn(nkv * ctx * hd, device=dev) * 0.5).to(torch.float16)
+            vc = (torch.randn(nkv * ctx * hd, device=dev) * 0.5).to(torch.float16)
+            scale = ctypes.c_float(1.0 / math.sqrt(hd))
+            nsplit = 16                                            # kindi/nanbeige.py:17
+            q = torch.randn(1, nh * hd, device=dev)
+            pos = torch.tensor([context - 1], dtype=torch.int32, device=dev)
+            part_o = torch.zeros(nh * nsplit * hd, device=dev)
+            part_ms = torch.zeros(nh * nsplit * 2, device=dev)
+            o = torch.empty(1, nh * hd, device=dev)
+            qp = torch.randn(prefill_tokens, nh * hd, device=dev)
+            op = torch.empty(prefill_tokens, nh * hd, device=dev)
+            flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # larger than the L2
+
+            def timed(fn, n=10):
+                best = []
+                for i in range(3 + n):
+                    flush.zero_()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    rc = fn()
+                    b.record()
+                    torch.cuda.synchronize()
+                    if rc != 0:
+                        raise RuntimeError("CUDA error %d" % rc)
+                    if i >= 3:
+                        best.append(a.elapsed_time(b) * 1000.0)
+                return round(statistics.median(best), 1)
+            dec = timed(lambda: lib.ref_attn_decode_g5(p(q), p(kc), p(vc), p(pos), ctx, scale, p(part_o), p(part_ms),
+                                                       nh * hd, nkv, nsplit, 1, p(o)))
+            pre = timed(lambda: lib.ref_fa_prefill_g5(p(qp), nh * hd, prefill_tokens, 0, p(kc), p(vc), ctx, scale, p(op),
+                                                      nkv))
+            return {"decode_attention_b1_ctx%d_us" % context: dec, "prefill_attention_%d_us" % prefill_tokens: pre,
+                    "what": "kindi/nbq.cu nbq_attn_part_g5 + nbq_attn_merge and kindi/nbq_fa.cu nbq_fa_prefill_g5, "
+                            "compiled unchanged for sm_100a, one layer, fp16 cache, L2 flushed before each launch, "
+                            "host-synchronised launches (a few microseconds of launch time are inside)"}
+    except Exception as e:                                          # noqa: BLE001
+        return {"error": str(e)[:200]}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)

@@ -645,16 +645,20 @@ __device__ __forceinline__ void kb_st8(bf16* p, const float* v) {
 // PLANES: the row is the sum of several planes (a decode step of many sequences). Without planes (a prompt) a thread
 // keeps few registers, so that most rows of a prompt are resident at once. Each thread requests its first item's
 // elements before it does anything else: those loads, the row's angles and its page lookup then wait side by side.
-template <typename TIN, typename T, bool PLANES>
+// TABLE: the cosines and sines of every row's angles were computed once for the step (k_rope_table: the same
+// expressions, so the same bits) and are read from there, 64 bytes per item beside the item's own loads; without it
+// each block computes its row's and shares them through shared memory.
+template <typename TIN, typename T, bool PLANES, bool TABLE = false>
 __global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const TIN* __restrict__ in, int n_planes,
         size_t plane_stride, int ld_in, T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
         const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
-        int hd, KbCacheView cv, int* status) {
+        int hd, KbCacheView cv, int* status, const float2* __restrict__ cs_table) {
     extern __shared__ float2 cs[];                  // [rot / 2]: (cos, sin) of the row's angles
     kb_pdl_launch();
     kb_pdl_wait();
     const int t = blockIdx.x;
     const int half = rot / 2;
+    const float2* cst = TABLE ? cs_table + (size_t)t * half : nullptr;
     const TIN* row = in + (size_t)t * ld_in;
     auto rd8 = [&](int e, float* v) {                // elements e .. e + 7 of the row: the planes added in order
         kb_ld8(row + e, v);
@@ -692,12 +696,22 @@ __global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const T
         }
     };
     float a[8], b[8];
-    if ((int)threadIdx.x < n_items) load_item(threadIdx.x, a, b);
+    float4 k4[4];                                    // TABLE: (cos, sin) of this thread's first item's eight pairs
+    if ((int)threadIdx.x < n_items) {
+        load_item(threadIdx.x, a, b);
+        if (TABLE && (int)threadIdx.x < n_rot) {
+            const float4* kp = (const float4*)(cst + ((int)threadIdx.x % per_head) * 8);
+#pragma unroll
+            for (int j = 0; j < 4; j++) k4[j] = kp[j];
+        }
+    }
 
     const int p = pos[t];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const float ang = __fmul_rn((float)p, inv_freq[i]);
-        cs[i] = make_float2(cosf(ang), sinf(ang));
+    if (!TABLE) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float ang = __fmul_rn((float)p, inv_freq[i]);
+            cs[i] = make_float2(cosf(ang), sinf(ang));
+        }
     }
     T* kdst = nullptr;
     T* vdst = nullptr;
@@ -711,10 +725,17 @@ __global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const T
             vdst = (T*)cv.pool + kb_kv_offset(cv, page, 1, 0, p % KB_PAGE);
         }
     }
-    __syncthreads();
+    if (!TABLE) __syncthreads();
     const size_t head_stride = (size_t)KB_PAGE * hd;       // from one key/value head to the next inside a page
     for (int it = threadIdx.x; it < n_items; it += blockDim.x) {
-        if (it != (int)threadIdx.x) load_item(it, a, b);
+        if (it != (int)threadIdx.x) {
+            load_item(it, a, b);
+            if (TABLE && it < n_rot) {
+                const float4* kp = (const float4*)(cst + (it % per_head) * 8);
+#pragma unroll
+                for (int j = 0; j < 4; j++) k4[j] = kp[j];
+            }
+        }
         if (it < n_rot) {
             const int h = it / per_head, i = (it % per_head) * 8;
             T* dst;
@@ -724,7 +745,9 @@ __global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const T
             float lo[8], hi[8];
 #pragma unroll
             for (int c = 0; c < 8; c++) {
-                const float2 k = cs[i + c];
+                float2 k;
+                if (TABLE) k = (c & 1) ? make_float2(k4[c >> 1].z, k4[c >> 1].w) : make_float2(k4[c >> 1].x, k4[c >> 1].y);
+                else k = cs[i + c];
                 lo[c] = __fsub_rn(__fmul_rn(a[c], k.x), __fmul_rn(b[c], k.y));
                 hi[c] = __fadd_rn(__fmul_rn(b[c], k.x), __fmul_rn(a[c], k.y));
             }
@@ -744,11 +767,32 @@ __global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const T
     }
 }
 
+// (cos, sin) of angle = float(pos[t]) * inv_freq[i] for every row t and pair i of a step: the angles are the same in
+// every layer, so a step computes them once and its rotate-and-store kernels read them (float2 [T][half])
+__global__ void k_rope_table(const int* __restrict__ pos, const float* __restrict__ inv_freq, int half, int T,
+                             float2* __restrict__ out) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= T * half) return;
+    const float ang = __fmul_rn((float)pos[e / half], inv_freq[e % half]);
+    out[e] = make_float2(cosf(ang), sinf(ang));
+}
+
+extern "C" int kb_rope_table(const int* pos, const float* inv_freq, int rot, int T, void* out, cudaStream_t st) {
+    const int half = rot / 2;
+    if (T <= 0 || half <= 0) return 0;
+    kb_launch(k_rope_table, (T * half + 255) / 256, 256, 0, st, pos, inv_freq, half, T, (float2*)out);
+    KB_LAUNCH_RET();
+}
+
 // in: [n_planes][T][ld_in] (the planes are summed in order); in_dtype may be 32-bit planes with a bf16 cache / qout
+// cs_table (may be null): float2 [T][rot / 2] made by kb_rope_table for these rows; used where the kernel form takes it
 extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in,
                              void* qout, int dtype, int ldq, const float* inv_freq, int rot, const int* pos,
                              const int* seq, const int* slot, int T, int nh, int nkv, int hd, void* pool,
-                             const int* table, int table_stride, int n_pages, int* status, cudaStream_t st) {
+                             const int* table, int table_stride, int n_pages, int* status, cudaStream_t st,
+                             const void* cs_table) {
     if (T <= 0) return 0;
     KbCacheView cv{pool, table, table_stride, n_pages, nkv, hd};
     dim3 grid(T, nh + 2 * nkv);
@@ -760,15 +804,25 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
     const bool by_row8 = by_row && rot % 16 == 0 && hd % 8 == 0 && ld_in % 8 == 0 && ldq % 8 == 0 &&
                          plane_stride % 8 == 0 && ((uintptr_t)in % (8 * in_el)) == 0 &&
                          ((uintptr_t)qout % (8 * out_el)) == 0 && ((uintptr_t)pool % (8 * out_el)) == 0;
+    const float2* cst = (const float2*)cs_table;
+    const bool tab = by_row8 && cst && ((uintptr_t)cst % 16) == 0;
 #define KB_RS(TIN, T_)                                                                                        \
-    if (by_row8 && n_planes > 1)                                                                              \
+    if (by_row8 && n_planes > 1 && tab)                                                                       \
+        kb_launch(k_rope_store_row8<TIN, T_, true, true>, T, 256, 0, st,                                      \
+                  (const TIN*)in, n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos,  \
+                  seq, slot, nh, nkv, hd, cv, status, cst);                                                   \
+    else if (by_row8 && tab)                                                                                  \
+        kb_launch(k_rope_store_row8<TIN, T_, false, true>, T, 256, 0, st,                                     \
+                  (const TIN*)in, n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos,  \
+                  seq, slot, nh, nkv, hd, cv, status, cst);                                                   \
+    else if (by_row8 && n_planes > 1)                                                                         \
         kb_launch(k_rope_store_row8<TIN, T_, true>, T, 256, (size_t)(rot / 2) * sizeof(float2), st,           \
                   (const TIN*)in, n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos,  \
-                  seq, slot, nh, nkv, hd, cv, status);                                                        \
+                  seq, slot, nh, nkv, hd, cv, status, cst);                                                   \
     else if (by_row8)                                                                                         \
         kb_launch(k_rope_store_row8<TIN, T_, false>, T, 256, (size_t)(rot / 2) * sizeof(float2), st,          \
                   (const TIN*)in, n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos,  \
-                  seq, slot, nh, nkv, hd, cv, status);                                                        \
+                  seq, slot, nh, nkv, hd, cv, status, cst);                                                   \
     else if (by_row)                                                                                               \
         kb_launch(k_rope_store_row<TIN, T_>, T, 256, (size_t)(rot / 2) * sizeof(float2), st, (const TIN*)in,   \
                   n_planes, (size_t)plane_stride, ld_in, (T_*)qout, ldq, inv_freq, rot, pos, seq, slot, nh,   \

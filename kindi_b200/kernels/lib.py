@@ -37,7 +37,8 @@ _SIGS = {
                      c_void_p],
     "kb_rope_store": [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
-                      c_void_p],
+                      c_void_p, c_void_p],
+    "kb_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "kb_attn_generic": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -267,11 +268,24 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                out.stride(0), _stream()), "gemm_simt")
 
 
+def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, rot: int) -> torch.Tensor:
+    """(cos, sin) of float(pos[t]) * inv_freq[i] for every row and rotated pair: float32 [T, rot / 2, 2]. The angles of
+    a step are the same in every layer, so a step makes this once and hands it to ``rope_store``"""
+    _need_cuda(pos, inv_freq)
+    T = pos.numel()
+    assert pos.dtype == torch.int32 and inv_freq.dtype == torch.float32 and rot % 2 == 0
+    assert inv_freq.numel() >= max(1, rot // 2)
+    out = torch.empty((T, rot // 2, 2), dtype=torch.float32, device=pos.device)
+    _check(load().kb_rope_table(_p(pos), _p(inv_freq), rot, T, _p(out), _stream()), "rope_table")
+    return out
+
+
 def rope_store(qkv: torch.Tensor, qout: torch.Tensor, inv_freq: torch.Tensor, rot: int, pos, seq, slot, nh: int,
                nkv: int, hd: int, pool: Optional[torch.Tensor], table: torch.Tensor, n_pages: int,
-               status: torch.Tensor) -> None:
+               status: torch.Tensor, angles: Optional[torch.Tensor] = None) -> None:
     """qkv: [T, (nh + 2 nkv) hd], or 32-bit planes [S, T, ...] that are summed. Query heads are rotated into qout
-    ([T, >= nh hd]; may be qkv itself), keys are rotated and stored in the cache, values are stored"""
+    ([T, >= nh hd]; may be qkv itself), keys are rotated and stored in the cache, values are stored. ``angles``: what
+    ``rope_table`` made for these rows (optional: without it the kernel computes the cosines and sines itself)"""
     _need_cuda(qkv, qout, inv_freq, pool, table)
     planes = qkv.shape[0] if qkv.dim() == 3 else 1
     T = qkv.shape[-2]
@@ -280,9 +294,12 @@ def rope_store(qkv: torch.Tensor, qout: torch.Tensor, inv_freq: torch.Tensor, ro
     if pool is not None:
         assert pool.dtype == qout.dtype and pool.is_contiguous()
     pstride = qkv.stride(0) if qkv.dim() == 3 else 0
+    if angles is not None:
+        assert angles.dtype == torch.float32 and angles.is_contiguous() and angles.shape == (T, rot // 2, 2)
     _check(load().kb_rope_store(_p(qkv), dt(qkv), planes, pstride, qkv.stride(-2), _p(qout), dt(qout),
                                 qout.stride(0), _p(inv_freq), rot, _p(pos), _p(seq), _p(slot), T, nh, nkv, hd,
-                                _p(pool), _p(table), table.stride(0), n_pages, _p(status), _stream()), "rope_store")
+                                _p(pool), _p(table), table.stride(0), n_pages, _p(status), _stream(), _p(angles)),
+           "rope_store")
 
 
 def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nkv: int, hd: int, scale: float,

@@ -69,6 +69,8 @@ class StepContext:
     fast: bool = True                  # bfloat16 serving kernels (False: the true 32-bit path)
     graph: bool = False                # the launches are being recorded for replay: host-side numbers (h_*,
                                        # max_kv) are not available and nothing may depend on them
+    scratch: Dict[Any, Any] = field(default_factory=dict)     # what parts keep for the rest of this step (a table that
+                                                              # is the same in every layer is made once)
 
 
 @dataclass

@@ -21,12 +21,21 @@ class RotationEncoding(PositionEncoding):
     """a rotation of the pairs (i, i + rotary_dim / 2) by pos * inv_freq[i]; subclasses set ``inv_freq`` (float32
     ``[max(1, rotary_dim / 2)]`` on the device) and ``rotary_dim`` (even, at most the head size; 0 rotates nothing)"""
 
+    # a hashable name of the frequency table when parts of other layers may have the very same one (then a step
+    # computes its rows' cosines and sines once and every such part uses them); None: this part's table is its own
+    angles_key = None
+
     def rotation(self):
         return self.inv_freq, self.rotary_dim
 
     def encode_and_store(self, ctx, qkv, q_out, n_heads, n_kv_store, head_dim, pool, table, n_pages) -> None:
+        angles = None
+        if self.angles_key is not None and ctx.T >= 32 and self.rotary_dim >= 16:
+            angles = ctx.scratch.get(self.angles_key)
+            if angles is None:
+                angles = ctx.scratch[self.angles_key] = K.rope_table(ctx.pos, self.inv_freq, self.rotary_dim)
         K.rope_store(qkv, q_out, self.inv_freq, self.rotary_dim, ctx.pos, ctx.seq, ctx.slot, n_heads, n_kv_store,
-                     head_dim, pool if n_kv_store else None, table, n_pages, ctx.status)
+                     head_dim, pool if n_kv_store else None, table, n_pages, ctx.status, angles)
 
 
 class Rotary(RotationEncoding):
@@ -38,6 +47,7 @@ class Rotary(RotationEncoding):
             raise ValueError("rotary_dim must be even and positive, found %d" % self.rotary_dim)
         i = torch.arange(0, self.rotary_dim // 2, dtype=torch.float64)
         self.inv_freq = (self.base ** (-2.0 * i / self.rotary_dim)).to(torch.float32).to(device)
+        self.angles_key = ("rotary", self.base, self.rotary_dim)
 
 
 class NoPosition(RotationEncoding):
