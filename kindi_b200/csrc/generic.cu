@@ -459,6 +459,7 @@ __global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t pl
     // angle of each thread is computed, before the wait for the kernel that produces the rows
     const int t = blockIdx.x, h = blockIdx.y;
     const int p = pos[t];
+    if (p < 0) return;                               // a padding row of a recorded step: nothing to rotate or store
     const TIN* src = in + (size_t)t * ld_in + (size_t)h * hd;
     T* dst;
     const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
@@ -537,6 +538,7 @@ __global__ void __launch_bounds__(256) k_rope_store_row(const TIN* __restrict__ 
     kb_pdl_wait();
     const int t = blockIdx.x;
     const int p = pos[t];
+    if (p < 0) return;                               // a padding row of a recorded step (the whole block leaves)
     const int half = rot / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const float ang = __fmul_rn((float)p, inv_freq[i]);
@@ -657,6 +659,7 @@ __global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const T
     kb_pdl_launch();
     kb_pdl_wait();
     const int t = blockIdx.x;
+    if (pos[t] < 0) return;                          // a padding row of a recorded step (the whole block leaves)
     const int half = rot / 2;
     const float2* cst = TABLE ? cs_table + (size_t)t * half : nullptr;
     const TIN* row = in + (size_t)t * ld_in;
@@ -858,6 +861,7 @@ __global__ void __launch_bounds__(128) k_attn_generic(const T* __restrict__ q, i
     const int t = (int)(item / nh), h = (int)(item % nh);
     const int hk = h / group;
     const int p_q = pos[t];
+    if (p_q < 0) return;                             // a padding row of a recorded step (the whole warp leaves)
     const int s = slot[seq[t]];
     const T* qr = q + (size_t)t * ldq + (size_t)h * hd;
     for (int d = lane; d < hd; d += 32) qs[warp][d] = __fmul_rn(kb_to_f<T>(qr[d]), scale);

@@ -25,7 +25,7 @@ class StepEntry:
 
 @dataclass
 class PackedStep:
-    T: int
+    T: int                            # rows of the step, padding rows included
     B: int
     R: int
     meta: np.ndarray                  # int32, all segments one after another
@@ -53,7 +53,10 @@ def layout(T: int, B: int, R: int) -> Tuple[dict, int]:
     return off, at
 
 
-def pack(entries: Sequence[StepEntry], length_before: Sequence[int]) -> PackedStep:
+def pack(entries: Sequence[StepEntry], length_before: Sequence[int], pad_rows_to: int = 0) -> PackedStep:
+    """``pad_rows_to``: the step gets at least this many rows; the rows past the sequences' tokens are padding (token
+    0, position -1, no sequence's row range holds them): they are computed and thrown away, change no cache and no
+    other row, and let steps of different lengths share one recorded launch sequence"""
     if not entries:
         raise ValueError("a step needs at least one sequence")
     slots = [e.slot for e in entries]
@@ -62,7 +65,8 @@ def pack(entries: Sequence[StepEntry], length_before: Sequence[int]) -> PackedSt
     q_len = [len(e.tokens) for e in entries]
     if min(q_len) < 1:
         raise ValueError("every sequence of a step brings at least one token")
-    B, T = len(entries), sum(q_len)
+    B, T_real = len(entries), sum(q_len)
+    T = max(T_real, pad_rows_to)
     rows: List[int] = []
     q_start = [0]
     for e, n in zip(entries, q_len):
@@ -89,6 +93,7 @@ def pack(entries: Sequence[StepEntry], length_before: Sequence[int]) -> PackedSt
         a, n = off[name]
         return meta[a:a + n]
     tok, pos, seq = seg("tok"), seg("pos"), seg("seq")
+    pos[T_real:] = -1
     kv_len = []
     for b, (e, n) in enumerate(zip(entries, q_len)):
         a = q_start[b]

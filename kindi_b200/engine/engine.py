@@ -46,10 +46,11 @@ class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, ctx: int = 24576, dtype: str = "bfloat16",
                  max_batch: int = 64, device: str = "cuda:0", spec: Optional[ModelSpec] = None,
                  tensors: Optional[Mapping[str, torch.Tensor]] = None, cuda_graphs: bool = True,
-                 max_step_tokens: int = 8192, log=None):
+                 max_step_tokens: int = 8192, prompt_graph_tokens: int = 512, log=None):
         """``model_dir``: a folder with config.json and safetensors files; or give ``spec`` and ``tensors``
         directly. ``ctx``: the most tokens all live sequences hold together (rounded up per sequence to the cache
-        page); it sizes the cache, like the reference's ``ctx`` (``kindi/nanbeige.py:245``)."""
+        page); it sizes the cache, like the reference's ``ctx`` (``kindi/nanbeige.py:245``). ``prompt_graph_tokens``:
+        prompt steps of up to this many tokens are recorded too, padded to a multiple of 64 rows (0: never)."""
         if dtype not in _DTYPES:
             raise EngineError("dtype must be 'bfloat16' or 'float32', not %r" % (dtype,))
         if not torch.cuda.is_available():
@@ -86,9 +87,11 @@ class Engine:
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[tuple, "_StepGraph"] = {}
         self.graph_replays = 0
         self._graph_warm = set()
+        self.prompt_graph_tokens = max(0, int(prompt_graph_tokens))
+        self.prompt_graphs_kept = 12                   # the most recorded prompt shapes kept (each holds its buffers)
 
     def _plan_memory(self, spec: ModelSpec, tensors) -> Dict[str, int]:
         """what the engine will hold on the device, counted before anything is allocated: the weights (twice the
@@ -161,7 +164,20 @@ class Engine:
                 if n + len(e.tokens) > limit:
                     raise EngineError("the sequence in slot %d would reach %d positions; the model's configuration "
                                       "allows %d (max_position_embeddings)" % (e.slot, n + len(e.tokens), limit))
-        ps = pack(entries, before)
+        # Recorded steps. The steady decode shape (one token and one wanted row per sequence) is recorded once per
+        # batch size and replayed (the reference records one graph per token too, kindi/nanbeige.py:728-734). Short
+        # prompt steps are bound by the host's launch-by-launch issue, not by the GPU: they are padded to a multiple
+        # of 64 rows and recorded per (rows, sequences, wanted rows). Lengths, slots, row ranges and tokens are read
+        # from device memory by the kernels, so a recording serves every step of its shape.
+        n_tok = sum(len(e.tokens) for e in entries)
+        key = None
+        if self.cuda_graphs:
+            if n_tok == len(entries):
+                if all(e.want == (0,) for e in entries):
+                    key = ("decode", len(entries))
+            elif n_tok <= self.prompt_graph_tokens and not tokens_from_previous:
+                key = ("prompt", (n_tok + 63) // 64 * 64, len(entries), sum(len(e.want) for e in entries))
+        ps = pack(entries, before, pad_rows_to=key[1] if key and key[0] == "prompt" else 0)
         reserved = []
         try:
             for e, new_len in zip(entries, ps.h_kv_len):
@@ -169,17 +185,20 @@ class Engine:
                 reserved.append(e.slot)
         except CacheFull as ex:
             raise CacheFull("%s while storing %d new tokens; the cache holds %d tokens (ctx = %d)"
-                            % (ex, ps.T, cache.tokens_held(), self.ctx)) from None
+                            % (ex, n_tok, cache.tokens_held(), self.ctx)) from None
         cache.flush()
         graph = None
-        if ps.decode and self.cuda_graphs and ps.R == ps.B and all(e.want == (0,) for e in entries):
-            # the steady decode shape: one token and one wanted row per sequence. The launch sequence is recorded
-            # once per batch size and replayed (the reference records one graph per token too,
-            # kindi/nanbeige.py:728-734); lengths, slots and tokens are read from device memory by the kernels
-            graph = self._graphs.get(ps.B)
-            if graph is None and ps.B in self._graph_warm:
-                graph = self._graphs[ps.B] = _DecodeGraph(self, ps)
-            self._graph_warm.add(ps.B)
+        if key is not None:
+            graph = self._graphs.get(key)
+            if graph is None and key in self._graph_warm:
+                if key[0] == "prompt":
+                    kept = [k for k in self._graphs if k[0] == "prompt"]
+                    if len(kept) >= self.prompt_graphs_kept:
+                        del self._graphs[kept[0]]              # the oldest recorded prompt shape makes room
+                graph = self._graphs[key] = _StepGraph(self, ps)
+            self._graph_warm.add(key)
+            if graph is None and ps.T != n_tok:
+                ps = pack(entries, before)                     # not recorded (yet): run it without the padding rows
         picked = None
         if graph is not None:
             logits = graph.replay(ps, tokens_from_previous)
@@ -248,10 +267,12 @@ class Engine:
             def seg0(name):
                 a, m = ps.off[name]
                 return dev[a:a + m]
+            # a recording: no host-side numbers; max_q is the most rows a sequence can bring (all the step's rows)
             return StepContext(T=ps.T, B=ps.B, tok=seg0("tok"), pos=seg0("pos"), seq=seg0("seq"), slot=seg0("slot"),
                                q_start=seg0("q_start"), kv_len=seg0("kv_len"), h_slot=None, h_q_start=None,
-                               h_kv_len=None, decode=True, max_q=1, max_kv=0, dtype=self.dtype, device=self.device,
-                               status=self.status, cache=self.cache, fast=self.dtype == torch.bfloat16, graph=True)
+                               h_kv_len=None, decode=ps.decode, max_q=1 if ps.decode else ps.T, max_kv=0,
+                               dtype=self.dtype, device=self.device, status=self.status, cache=self.cache,
+                               fast=self.dtype == torch.bfloat16, graph=True)
         n = ps.meta.size
         cap = 1 << max(6, (n - 1).bit_length())
         pin = self._pinned.get(cap)
@@ -367,8 +388,9 @@ def _to_run_dtype(t: torch.Tensor, run_dtype: str) -> torch.Tensor:
     return t.to(target_dtype(t.dtype, run_dtype))
 
 
-class _DecodeGraph:
-    """the recorded launch sequence of one decode step for a batch of B sequences, over fixed device buffers"""
+class _StepGraph:
+    """the recorded launch sequence of one step shape (a decode step of B sequences, or a prompt step of so many rows,
+    sequences and wanted rows), over fixed device buffers"""
 
     def __init__(self, engine: Engine, ps: PackedStep):
         self.engine = engine
@@ -393,7 +415,8 @@ class _DecodeGraph:
         try:
             with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
                 self.logits = engine.model.forward(ctx, rows)
-                self.picked = engine.pick(self.logits, _GREEDY)                 # the greedy pick rides along
+                # the greedy pick rides along (a step that wants no row has nothing to pick)
+                self.picked = engine.pick(self.logits, _GREEDY) if self.logits is not None else None
         finally:
             if was_on:
                 gc.enable()

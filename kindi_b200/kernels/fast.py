@@ -98,6 +98,28 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
     return best
 
 
+@functools.lru_cache(maxsize=4096)
+def _prefill_split(m: int, n: int, k: int):
+    """(columns of a tile, ways to split K) for a product of a few hundred rows whose consumer takes 32-bit planes (the
+    output and down products of a short prompt or a wide decode step), or None when one plane from _prefill_tile is as
+    good. With so few rows there are fewer 128-row tiles than SMs, and a tile's K loop is long (164 blocks for a
+    feed-forward of 10496): splitting K fills the SMs, at the price of writing and re-reading a plane per split."""
+    kb = -(-k // 64)
+    best, best_cost = None, None
+    for bn in (256, 192, 128):
+        units = -(-m // 128) * -(-n // bn)
+        t_kb = max(0.276 * bn / 256.0, 1.15e-3 * (128 + bn))
+        for sp in (1, 2, 3, 4, 6, 8):
+            kbps = -(-kb // sp)
+            if sp > 1 and (kbps < 8 or units * sp > 2 * N_SM):
+                continue
+            z = -(-kb // kbps)
+            cost = -(-units * z // N_SM) * (kbps * t_kb + 0.004 * bn + 2.0) + z * m * n * 8 / 6.6e6
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = (bn, sp), cost
+    return best if best is not None and best[1] > 1 else None
+
+
 _PAIR_SCRATCH = {}         # device -> (partial tiles, flags): scratch of tiles that two pairs of SMs finish together
 
 
@@ -143,6 +165,13 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
         out = torch.empty((s, m, n), dtype=torch.float32, device=a.device)
         K.gemm_tc(a, w, out, swap=True, bn=bn, splits=want, status=status)
         return out
+    if m < 1024:
+        plan = _prefill_split(m, n, k)
+        if plan is not None:
+            bn, want = plan
+            out = torch.empty((K.gemm_tc_splits(k, want), m, n), dtype=torch.float32, device=a.device)
+            K.gemm_tc(a, w, out, swap=False, bn=bn, splits=want, status=status)
+            return out
     out = torch.empty((1, m, n), dtype=torch.float32, device=a.device)
     _prefill_product(a, w, out[0], status, False)
     return out
@@ -152,8 +181,8 @@ def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor
     """out (bf16 [M, F]) = silu(g) * u for a prompt-sized step, finished inside the product's epilogue; w_grouped
     [2F, K] holds 16 gate rows then the 16 up rows of the same outputs, group after group. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
-    if m <= SMALL_M or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
-        return False
+    if m <= 32 or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
+        return False        # (up to 32 rows the decode form with SwiGLU inside is the faster one)
     _prefill_product(a, w_grouped, out, status, True)
     return True
 
@@ -195,8 +224,7 @@ def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages
         K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table,
                    n_pages, decode=True, grid_x=splits, status=ctx.status)
         return True
-    if ctx.graph:
-        return False
+    # (in a recording ctx.max_q is the most rows a sequence can bring: the grid then has tiles to spare, which leave)
     if g <= 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
         # prompt-sized steps: the tcgen05 kernel (S and O in tensor memory)
         K.attn_tc(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,

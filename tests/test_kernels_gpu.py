@@ -43,6 +43,8 @@ TC_CASES = [
     (300, 700, 200, False, 160, 1), (129, 500, 136, False, 192, 1), (512, 2560, 320, False, 224, 1),
     (260, 2560, 200, False, 144, 1), (140, 360, 72, False, 176, 1), (300, 3584, 264, False, 208, 1),
     (129, 1000, 136, False, 240, 1),
+    # the prefill form with K split into planes (a few hundred rows: fewer tiles than SMs)
+    (256, 2560, 10496, False, 256, 6), (300, 700, 1096, False, 128, 3), (129, 500, 4096, False, 192, 8),
     (1, 128, 64, True, 16, 1), (8, 384, 2560, True, 16, 1), (8, 384, 2560, True, 16, 5), (17, 200, 264, True, 32, 3),
     (64, 331 * 8, 1096, True, 64, 4), (100, 256, 4096, True, 128, 8), (5, 130, 72, True, 16, 2),
 ]
@@ -349,6 +351,23 @@ def test_prompt_products_as_the_engine_chooses_them(K):
     gg, uu = a.float() @ wg.float().T, a.float() @ wu.float().T
     assert _rel(h.float(), gg / (1 + torch.exp(-gg)) * uu) < 1e-2
     assert all(int(f.abs().sum().item()) == 0 for _, f in fast._PAIR_SCRATCH.values())
+
+
+def test_products_of_a_few_hundred_rows_split_k(K):
+    """the output and down products of a short prompt (129 to 511 rows) come as several planes of a K split that fills
+    the SMs; their sum is the product"""
+    from kindi_b200.kernels import fast
+    assert fast._prefill_split(256, 2560, 10496)[1] > 1 and fast._prefill_split(2048, 2560, 10496) is None
+    g = torch.Generator(device="cuda").manual_seed(6)
+    st = _status()
+    for M, N, K_ in ((256, 2560, 10496), (129, 2560, 2560), (500, 2560, 10496), (384, 1000, 4104)):
+        a = (torch.randn(M, K_, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(N, K_, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        planes = fast.gemm_planes(a, w, st)
+        assert int(st.item()) == 0 and planes.shape[1:] == (M, N)
+        if fast._prefill_split(M, N, K_) is not None:
+            assert planes.shape[0] > 1
+        assert _rel(planes.sum(0), a.double() @ w.double().T) < 1e-5
 
 
 @pytest.mark.parametrize("M,N,K_,bn", [(256, 256, 64, 128), (2048, 2560, 1096, 160), (300, 700, 200, 192),

@@ -268,3 +268,63 @@ def test_window_layers_keep_a_small_pool_over_a_long_sequence(tmp_path):
         err = tiny.rel_err(np.stack([got[(r, i)] for i in have]), want[r][have])
         assert err <= TOL["bfloat16"], (r, err)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompt_steps_are_recorded_and_padding_changes_nothing(tmp_path, dtype):
+    """prompt steps of up to 512 tokens are padded to a multiple of 64 rows and replayed from a recording once their
+    shape has been seen twice. Prompts of 100, 90, 128, 65 and 70 tokens share the 128-row recording, pairs of unequal
+    prompts another; a step that wants no row is recorded too. Every logit equals the plain model; in 32-bit the
+    recorded steps give the same bits as an engine that records nothing; the padding rows store nothing (the next
+    tokens of each sequence still see exactly their own keys)"""
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.engine.engine import Engine
+    cfg = tiny.TINY["E"][0]
+    folder = tiny.make_needle_model(tmp_path, cfg, seed=31, dtype=dtype, name="needleE")
+    vocab = cfg["vocab_size"]
+    m = P.load_model(folder)
+    rng = random.Random(9)
+    eng = Engine(folder, ctx=4096, dtype=dtype, max_batch=4)
+    plain_eng = Engine(folder, ctx=4096, dtype=dtype, max_batch=4, cuda_graphs=False)
+
+    def run(e, groups, follow=3):
+        """each group of prompts is one step that wants the last row of each; then `follow` tokens one by one"""
+        out = []
+        for group in groups:
+            slots = [e.alloc() for _ in group]
+            k = [len(t) - follow for t in group]
+            logits = e.step([StepEntry(s, tuple(t[:n]), (n - 1,)) for s, t, n in zip(slots, group, k)])
+            rows = [[logits[i].cpu().numpy()] for i in range(len(group))]
+            for j in range(follow):
+                lg = e.step([StepEntry(s, (t[n + j],), (0,)) for s, t, n in zip(slots, group, k)])
+                for i in range(len(group)):
+                    rows[i].append(lg[i].cpu().numpy())
+            e.check_status()
+            for s in slots:
+                e.free(s)
+            out.append([np.stack(r) for r in rows])
+        return out
+
+    lengths = [[103], [93], [131], [68], [73], [40, 71], [64, 9], [8, 100], [200], [260], [300]]
+    groups = [[tiny.needle_request(vocab, n, 1, n - 5, rng) for n in g] for g in lengths]
+    got = run(eng, groups)
+    assert sum(1 for k in eng._graphs if k[0] == "prompt") >= 2 and eng.graph_replays >= 6
+    same = run(plain_eng, groups)
+    for g, mine, other in zip(groups, got, same):
+        for toks, a, b in zip(g, mine, other):
+            want = P.forward(m, toks).numpy()[len(toks) - 4:]
+            assert tiny.rel_err(a, want) <= TOL[dtype], (len(toks), tiny.rel_err(a, want))
+            if dtype == "float32":
+                assert np.array_equal(a, b), len(toks)
+    # a prompt brought in two steps, the first of which wants nothing (recorded at its second occurrence)
+    for n in (150, 170, 190):
+        toks = tiny.needle_request(vocab, n, 2, n - 20, rng)
+        s = eng.alloc()
+        assert eng.step([StepEntry(s, tuple(toks[:100]), ())]) is None
+        lg = eng.step([StepEntry(s, tuple(toks[100:]), (n - 101,))])[0].cpu().numpy()
+        eng.check_status()
+        eng.free(s)
+        assert tiny.rel_err(lg, P.forward(m, toks).numpy()[-1]) <= TOL[dtype]
+    assert ("prompt", 128, 1, 0) in eng._graphs
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
