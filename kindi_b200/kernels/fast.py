@@ -9,13 +9,9 @@ from typing import Optional
 import torch
 
 from . import lib as K
+from .device import DEVICE as DEV
 
-N_SM = 148                 # B200: 2 dies x 74 SMs (replaced by the device's own count when a GPU is present)
-try:
-    if torch.cuda.is_available():
-        N_SM = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-except Exception:                                       # noqa: BLE001
-    pass
+N_SM = DEV.n_sm            # the device's own count (148 on a B200)
 SMALL_M = 128              # up to here the weights go through the 128-row side of the MMA ("swap" form)
 
 
@@ -41,14 +37,14 @@ def _splits_for(m: int, n: int, k: int, bn: int) -> int:
     plus what the 32-bit planes cost to write and to read again by the consumer (they grow with the batch)"""
     tiles = -(-n // 128) * -(-m // bn)
     total_kb = -(-k // 64)
-    us_per_kb = 16384.0 / (6.6e6 / N_SM)
+    us_per_kb = 16384.0 / (DEV.hbm_bytes_per_us / N_SM)
     best, best_cost = 1, None
     for s in range(1, min(16, total_kb) + 1):
         kbps = -(-total_kb // s)
         if -(-total_kb // kbps) != s or (s > 1 and kbps < 2):
             continue
         rounds = -(-tiles * s // N_SM)
-        cost = rounds * (kbps + 0.5) * us_per_kb + s * m * n * 4 / 6.6e6
+        cost = rounds * (kbps + 0.5) * us_per_kb + s * m * n * 4 / DEV.hbm_bytes_per_us
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -76,7 +72,7 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
             if swiglu and bn % 32:
                 continue
             units = -(-m // (128 * mt)) * -(-n // bn)
-            t_kb = max(0.276 * mt * bn / 256.0, 1.15e-3 * (128 * mt + bn))
+            t_kb = max(DEV.mma_us_per_kblock_128x256 * mt * bn / 256.0, DEV.l2_us_per_operand_row * (128 * mt + bn))
             epilogue = (0.02 if mt == 2 else 0.004) * bn * mt
             cost = -(-units // N_SM) * (kb * t_kb + epilogue)
             if best_cost is None or cost < best_cost:
@@ -85,13 +81,13 @@ def _prefill_tile(m: int, n: int, k: int, swiglu: bool = False):
         pairs = N_SM // 2
         for bn in (256, 192, 128):
             units = -(-m // 256) * -(-n // bn)
-            t_kb = max(0.37 * bn / 256.0, 0.33)         # (narrower tiles were not measured faster than 0.33 us)
+            t_kb = max(DEV.pair_us_per_kblock_256x256 * bn / 256.0, DEV.pair_us_per_kblock_floor)
             cost = -(-units // pairs) * (kb * t_kb + 1.5)
             if cost < best_cost:
                 best, best_cost = ("pair", bn, False), cost
             # (dealt out, the pairs that share an operand tile read it some K blocks apart in time: both operands have
             # to stay in the L2 meanwhile, or the product waits for DRAM: 5120 x 13824 weights, 288 us against 226)
-            if not swiglu and units >= pairs and (m + n) * k * 2 <= 100e6:
+            if not swiglu and units >= pairs and (m + n) * k * 2 <= DEV.l2_resident_bytes:
                 cost = units * kb / pairs * t_kb + 10.0
                 if cost < best_cost:
                     best, best_cost = ("pair", bn, True), cost
@@ -108,13 +104,13 @@ def _prefill_split(m: int, n: int, k: int):
     best, best_cost = None, None
     for bn in (256, 192, 128):
         units = -(-m // 128) * -(-n // bn)
-        t_kb = max(0.276 * bn / 256.0, 1.15e-3 * (128 + bn))
+        t_kb = max(DEV.mma_us_per_kblock_128x256 * bn / 256.0, DEV.l2_us_per_operand_row * (128 + bn))
         for sp in (1, 2, 3, 4, 6, 8):
             kbps = -(-kb // sp)
             if sp > 1 and (kbps < 8 or units * sp > 2 * N_SM):
                 continue
             z = -(-kb // kbps)
-            cost = -(-units * z // N_SM) * (kbps * t_kb + 0.004 * bn + 2.0) + z * m * n * 8 / 6.6e6
+            cost = -(-units * z // N_SM) * (kbps * t_kb + 0.004 * bn + 2.0) + z * m * n * 8 / DEV.hbm_bytes_per_us
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = (bn, sp), cost
     return best if best is not None and best[1] > 1 else None
