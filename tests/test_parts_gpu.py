@@ -360,3 +360,123 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype, 
         assert eng.cache.slots.n_held == 0
     if eng.cuda_graphs:
         assert eng.graph_replays > 0                  # its decode steps were recorded and replayed
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# a whole toy ARCHITECTURE defined here and loaded from a model folder: config.json keys of its own (no attention
+# heads, a GELU feed-forward, an embedding scale, a logit scale and soft cap), registered with the package's registry;
+# the folder is written by the random-weights mode and read back by the engine like any other.
+def _toy_architecture():
+    from kindi_b200.config import (ConfigError, ConfigReader, LayerSpec, ModelSpec, PartSpec, default_schedule,
+                                   register_architecture, register_part)
+    from kindi_b200.parts.base import Branch, FeedForward
+    _toy_parts()                                                     # the running-mean mixer with state
+
+    class GeluMLP(FeedForward):
+        """gelu(W1 y + b1) W2, the tanh form, written with device-side PyTorch only (no host numbers)"""
+
+        @classmethod
+        def tensor_shapes(cls, spec, width):
+            f = int(spec["inner"])
+            return {"fc.weight": (f, width), "fc.bias": (f,), "proj.weight": (width, f)}
+
+        @classmethod
+        def tensor_init(cls, spec, width):
+            return {"fc.bias": "zero"}
+
+        def __init__(self, spec, width, weights, *, dtype, device):
+            super().__init__(spec, width, weights, dtype=dtype, device=device)
+            self.w1, self.b1, self.w2 = (weights(n).float() for n in ("fc.weight", "fc.bias", "proj.weight"))
+
+        def forward(self, ctx, y):
+            h = torch.nn.functional.gelu(y.float() @ self.w1.T + self.b1, approximate="tanh")
+            return Branch((h @ self.w2.T)[None].contiguous())
+
+    def read(raw):
+        r = ConfigReader(raw)
+        r.ignore("architectures", "model_type")
+        if r.string("hidden_act") != "gelu_tanh":
+            raise ConfigError("config.json: the toy architecture has a tanh-GELU feed-forward only")
+        c = dict(width=r.integer("d_model"), layers=r.integer("n_layer"), vocab=r.integer("vocab_size"),
+                 inner=r.integer("d_inner"), eps=r.number("layer_norm_epsilon"), emb_scale=r.number("emb_scale", 1.0),
+                 logit_scale=r.number("logit_scale", 1.0), softcap=r.number("logit_softcap", None))
+        r.finish()
+        return c
+
+    def build(c):
+        norm = PartSpec("rmsnorm", {"eps": c["eps"]})
+        block = PartSpec("prenorm", {"norm1": norm, "mixer": PartSpec("toy_running_mean", {}), "norm2": norm,
+                                     "feed_forward": PartSpec("toy_gelu", {"inner": c["inner"]}),
+                                     "names": {"norm1": "ln_1.", "mixer": "mix.", "norm2": "ln_2.", "feed_forward": "mlp."}})
+        return ModelSpec(architecture="ToyMeanGeluLM", vocab_size=c["vocab"], width=c["width"],
+                         layers=tuple(LayerSpec(block, "h.%d." % i) for i in range(c["layers"])),
+                         schedule=default_schedule(c["layers"]), final_norm=norm, final_norm_prefix="ln_f.",
+                         embedding=PartSpec("table", {"name": "wte.weight", "vocab": c["vocab"], "scale": c["emb_scale"]}),
+                         head=PartSpec("linear", {"name": "head.weight", "vocab": c["vocab"], "scale": c["logit_scale"],
+                                                  "softcap": c["softcap"]}))
+
+    register_part("feed_forward", "toy_gelu", GeluMLP, replace=True)
+    register_architecture("ToyMeanGeluLM", build, read, replace=True)
+
+
+TOY_CONFIG = dict(architectures=["ToyMeanGeluLM"], hidden_act="gelu_tanh", d_model=48, n_layer=3, vocab_size=131,
+                  d_inner=80, layer_norm_epsilon=1e-5, emb_scale=6.0, logit_scale=0.5, logit_softcap=4.0)
+
+
+def _toy_architecture_plain(folder, tokens):
+    """whole sequence, float64, from the folder's files alone"""
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
+    c = TOY_CONFIG
+    n = len(tokens)
+    x = P.embedding(w["wte.weight"], tokens) * c["emb_scale"]
+    for i in range(c["n_layer"]):
+        p = "h.%d." % i
+        y = P.rms_norm(x, w[p + "ln_1.weight"], c["layer_norm_epsilon"])
+        mean = torch.cumsum(y, 0) / torch.arange(1, n + 1, dtype=torch.float64)[:, None]
+        x = x + mean @ w[p + "mix.mix.weight"].T
+        y = P.rms_norm(x, w[p + "ln_2.weight"], c["layer_norm_epsilon"])
+        h = torch.nn.functional.gelu(y @ w[p + "mlp.fc.weight"].T + w[p + "mlp.fc.bias"], approximate="tanh")
+        x = x + h @ w[p + "mlp.proj.weight"].T
+    z = (P.rms_norm(x, w["ln_f.weight"], c["layer_norm_epsilon"]) @ w["head.weight"].T) * c["logit_scale"]
+    return c["logit_softcap"] * torch.tanh(z / c["logit_softcap"])
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 1.5e-2)])
+def test_toy_architecture_from_a_model_folder(tmp_path, dtype, tol):
+    """another architecture is a registry entry: its folder (own config.json keys, own tensor names, a mixer with
+    state and no attention at all) is written by the random-weights mode, loaded by the engine, replayed whole, token
+    by token and in unequal batches, and generates; nothing of the package knows it"""
+    from kindi_b200 import Engine, write_random_model
+    from kindi_b200.config import ConfigError, model_from_dir
+    _toy_architecture()
+    folder = write_random_model(str(tmp_path / "toy"), TOY_CONFIG, seed=3, std=0.05, dtype=dtype)
+    cfg, spec = model_from_dir(folder)
+    assert cfg["width"] == 48 and spec.architecture == "ToyMeanGeluLM" and spec.head["softcap"] == 4.0
+    eng = Engine(folder, ctx=1024, dtype=dtype, max_batch=3)
+    assert not eng.cuda_graphs                                   # the running-mean mixer reads host numbers
+    reqs = tiny.random_requests(131, [40, 7, 90, 3, 66], seed=4)
+    want = {r: _toy_architecture_plain(folder, t).numpy() for r, t in reqs.items()}
+    assert max(np.abs(v).max() for v in want.values()) < 4.0     # the soft cap is at work
+    for steps in (tiny.trace_whole(reqs), tiny.trace_last_n(reqs, 32), tiny.trace_batched(reqs, batch=3, decode=10)):
+        out = str(tmp_path / ("a%d" % len(steps)))
+        tiny.run_replay(eng, steps, out)
+        got = tiny.collect(out, steps, 131)
+        for r, t in reqs.items():
+            mine = np.stack([got[(r, i)] for i in range(len(t))])
+            assert tiny.rel_err(mine, want[r]) < tol, (len(steps), r, tiny.rel_err(mine, want[r]))
+        eng.cache.check()
+    res = eng.generate_batch([reqs["r0"][:9], reqs["r2"][:30]], temperature=0.0, max_tokens=5, stop_token_ids=())
+    for prompt, toks in zip((reqs["r0"][:9], reqs["r2"][:30]), res.tokens):
+        seq = list(prompt)
+        for t in toks:
+            z = _toy_architecture_plain(folder, seq)[-1].numpy()
+            assert t == int(z.argmax()) or z.max() - z[t] < tol * np.abs(z).max()
+            seq.append(t)
+    # a key of another architecture in this folder's config.json is refused by this architecture's reader
+    import json
+    bad = dict(TOY_CONFIG, num_attention_heads=4)
+    (tmp_path / "bad").mkdir()
+    (tmp_path / "bad" / "config.json").write_text(json.dumps(bad))
+    with pytest.raises(ConfigError):
+        model_from_dir(str(tmp_path / "bad"))
