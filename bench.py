@@ -371,6 +371,7 @@ def main(argv=None) -> int:
                     help="also generate for 8 prompts of random lengths 128 to 2048, 256 tokens each, through the "
                          "Python entry point (the 16B-class configuration's workload)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement (for profiling runs)")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill (for profiling)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
@@ -411,7 +412,7 @@ def main(argv=None) -> int:
     mc = eng.config
     clocks = ClockSampler()
     clocks.start()
-    dev_ms, e2e_ms, launches, bytes_step = bench_decode(eng, a.batch, a.context, a.steps, a.warmup, True)
+    dev_ms, e2e_ms, launches, bytes_step = bench_decode(eng, a.batch, a.context, a.steps, a.warmup, not a.no_e2e)
     clk = clocks.stop()
     value = a.batch * 1000.0 / dev_ms
     out = {
@@ -429,9 +430,10 @@ def main(argv=None) -> int:
                    "cuda_graph": eng.graph_replays > 0},
         "clocks": clk,
         "gpu_launches": launches,
-        "e2e": {"value": round(a.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": 4 * layout(a.batch, a.batch, a.batch)[1], "d2h_bytes_per_step": 4 * a.batch + 4,
-                "ms_per_step": round(e2e_ms, 4)},
+        "e2e": None if e2e_ms is None else {
+            "value": round(a.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s",
+            "h2d_bytes_per_step": 4 * layout(a.batch, a.batch, a.batch)[1], "d2h_bytes_per_step": 4 * a.batch + 4,
+            "ms_per_step": round(e2e_ms, 4)},
         "roofline": {"bound": "hbm", "achieved": round(bytes_step / dev_ms / 1e6, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(bytes_step / dev_ms / 1e6 / pk["hbm_gbs"], 4),
                      "of": pk["source"], "bytes_per_step": int(bytes_step)},
