@@ -71,6 +71,8 @@ class Engine:
         self.ctx = int(ctx)
         self.max_batch = int(max_batch)
         self.max_step_tokens = max(64, int(max_step_tokens))     # longer steps are run in pieces of this many tokens
+        self.prompt_graph_tokens = max(0, int(prompt_graph_tokens)) if cuda_graphs else 0
+        self.prompt_graphs_kept = 12                   # the most recorded prompt shapes kept (each holds its buffers)
         self.plan = self._plan_memory(spec, tensors)
         if tensors is None:
             tensors = load_tensors(model_dir, expected_tensors(spec), run_dtype=dtype, device=str(self.device),
@@ -90,8 +92,6 @@ class Engine:
         self._graphs: Dict[tuple, "_StepGraph"] = {}
         self.graph_replays = 0
         self._graph_warm = set()
-        self.prompt_graph_tokens = max(0, int(prompt_graph_tokens))
-        self.prompt_graphs_kept = 12                   # the most recorded prompt shapes kept (each holds its buffers)
 
     def _plan_memory(self, spec: ModelSpec, tensors) -> Dict[str, int]:
         """what the engine will hold on the device, counted before anything is allocated: the weights (twice the
@@ -111,8 +111,11 @@ class Engine:
                                            self.max_step_tokens)
         widest = max([spec.width] + [s[0] for s in shapes.values() if len(s) == 2 and s[0] != spec.vocab_size])
         rows = min(self.max_step_tokens, self.ctx)
-        # residual + branch planes in 32-bit, the widest activation twice in the run dtype, logits of a decode batch
-        work = rows * (3 * spec.width * 4 + 2 * widest * max(el, 2)) + self.max_batch * spec.vocab_size * 4 * 2
+        # residual + branch planes in 32-bit, the widest activation twice in the run dtype, logits of a decode batch;
+        # every recorded prompt shape keeps buffers of its own for its rows
+        per_row = 3 * spec.width * 4 + 2 * widest * max(el, 2)
+        work = (rows + self.prompt_graphs_kept * self.prompt_graph_tokens) * per_row \
+            + self.max_batch * spec.vocab_size * 4 * 2
         plan = {"weights": weights, "cache": cache, "work": work, "total": weights + cache + work}
         free, total = torch.cuda.mem_get_info(self.device)
         plan["free"] = int(free)
