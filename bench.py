@@ -356,12 +356,109 @@ def reference_kernel_times(cfg, context: int, prefill_tokens: int):
         return {"error": str(e)[:200]}
 
 
+def bench_torch(cfg, layers: int, batch: int, context: int, steps: int, warmup: int, prefill_tokens: int):
+    """a comparison arm that is NOT the reference and not this library: the same model (same seeded weights, same
+    sizes) written with PyTorch's own operators - cuBLAS products, its fused attention over a dense bf16 cache, element
+    by element kernels for norm, rotation and SwiGLU - with the decode step recorded as a CUDA graph. What library code
+    gives on this GPU for the same metric; the formulas are those of tests/plain_model.py."""
+    import math
+    import torch
+    import torch.nn.functional as F
+    from kindi_b200.config import model_from_config
+    from kindi_b200.parts.model import expected_tensors, tensor_inits
+    from kindi_b200.weights.random_init import random_tensors
+    c = dict(cfg)
+    c["num_hidden_layers"] = layers
+    mc, spec = model_from_config(c)
+    w = random_tensors(expected_tensors(spec), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0",
+                       inits=tensor_inits(spec))
+    E, nh, nkv, hd, eps = mc.hidden_size, mc.num_attention_heads, mc.num_key_value_heads, mc.head_dim, mc.rms_norm_eps
+    wqkv = [torch.cat([w["model.layers.%d.self_attn.%s_proj.weight" % (i, n)] for n in "qkv"]) for i in range(layers)]
+    wgu = [torch.cat([w["model.layers.%d.mlp.%s_proj.weight" % (i, n)] for n in ("gate", "up")]) for i in range(layers)]
+    inv = (mc.rope_theta ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().cuda()
+
+    def norm(x, g):
+        return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)).to(torch.bfloat16) * g
+
+    def rope(x, pos):                                        # x [B, T, heads, hd], pos [B, T]
+        ang = pos[..., None].float() * inv
+        cs, sn = torch.cos(ang)[:, :, None], torch.sin(ang)[:, :, None]
+        a, b = x[..., : hd // 2].float(), x[..., hd // 2:].float()
+        return torch.cat([a * cs - b * sn, b * cs + a * sn], -1).to(torch.bfloat16)
+
+    def forward(tok, pos, kc, vc, lens):
+        """tok, pos [B, T]; caches [layers][B, nkv, ctx, hd]; lens = keys each sequence holds after this step (int)"""
+        B, T = tok.shape
+        x = w["model.embed_tokens.weight"][tok].float()
+        for i in range(layers):
+            p = "model.layers.%d." % i
+            y = norm(x, w[p + "input_layernorm.weight"])
+            qkv = y @ wqkv[i].T
+            q = rope(qkv[..., : nh * hd].view(B, T, nh, hd), pos)
+            k = rope(qkv[..., nh * hd: (nh + nkv) * hd].view(B, T, nkv, hd), pos)
+            v = qkv[..., (nh + nkv) * hd:].view(B, T, nkv, hd)
+            kc[i][:, :, lens - T: lens] = k.transpose(1, 2)
+            vc[i][:, :, lens - T: lens] = v.transpose(1, 2)
+            att = F.scaled_dot_product_attention(q.transpose(1, 2), kc[i][:, :, :lens], vc[i][:, :, :lens],
+                                                 is_causal=T > 1, enable_gqa=True)
+            x = x + (att.transpose(1, 2).reshape(B, T, nh * hd) @ w[p + "self_attn.o_proj.weight"].T).float()
+            y = norm(x, w[p + "post_attention_layernorm.weight"])
+            gu = y @ wgu[i].T
+            h = F.silu(gu[..., : gu.shape[-1] // 2].float()).to(torch.bfloat16) * gu[..., gu.shape[-1] // 2:]
+            x = x + (h @ w[p + "mlp.down_proj.weight"].T).float()
+        y = norm(x[:, -1], w["model.norm.weight"])
+        return (y @ w["lm_head.weight"].T).float().argmax(-1)
+
+    out = {}
+    # ---- decode: B sequences that hold `context` keys after the step; the step recorded as a CUDA graph
+    kc = [torch.randn(batch, nkv, context, hd, device="cuda").to(torch.bfloat16) for _ in range(layers)]
+    vc = [torch.randn(batch, nkv, context, hd, device="cuda").to(torch.bfloat16) for _ in range(layers)]
+    tok = torch.randint(0, mc.vocab_size, (batch, 1), device="cuda")
+    pos = torch.full((batch, 1), context - 1, device="cuda", dtype=torch.int64)
+    for _ in range(3):
+        forward(tok, pos, kc, vc, context)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        picked = forward(tok, pos, kc, vc, context)
+    for _ in range(max(3, warmup)):
+        g.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(steps):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    out["decode_ms"] = a.elapsed_time(b) / steps
+    del kc, vc, g
+    # ---- prefill of one prompt (eager: launch by launch, as PyTorch runs a model)
+    kc = [torch.zeros(1, nkv, prefill_tokens, hd, device="cuda", dtype=torch.bfloat16) for _ in range(layers)]
+    vc = [torch.zeros(1, nkv, prefill_tokens, hd, device="cuda", dtype=torch.bfloat16) for _ in range(layers)]
+    tok = torch.randint(0, mc.vocab_size, (1, prefill_tokens), device="cuda")
+    pos = torch.arange(prefill_tokens, device="cuda")[None]
+    ts = []
+    for i in range(8):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        forward(tok, pos, kc, vc, prefill_tokens)
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            ts.append(a.elapsed_time(b))
+    out["prefill_ms"] = statistics.median(ts)
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference", "torch"),
+                    help="ours; the reference (unavailable here, with its attention kernels timed); or 'torch': the same "
+                         "model written with PyTorch's own operators, a comparison that is neither")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--preset", default="3b", choices=sorted(PRESETS),
@@ -383,6 +480,18 @@ def main(argv=None) -> int:
         if kt is not None:
             line["kernel_level"] = kt
         print(json.dumps(line))
+        return 0
+    if a.impl == "torch" and a.gpus == 1:
+        name, base = PRESETS[a.preset]
+        layers = a.layers if a.layers > 0 else base["num_hidden_layers"]
+        r = bench_torch(base, layers, a.batch, a.context, a.steps, max(3, a.warmup), PREFILL_TOKENS)
+        print(json.dumps({"impl": "torch", "what": "the same model with PyTorch's own operators (cuBLAS, fused attention "
+                          "over a dense bf16 cache, the decode step as a CUDA graph): not the reference, not this library",
+                          "metric": "decode tokens/s (batch %d, context %d)" % (a.batch, a.context),
+                          "value": round(a.batch * 1000.0 / r["decode_ms"], 1), "unit": "tokens/s",
+                          "ms_per_step": round(r["decode_ms"], 4), "steps": a.steps, "layers": layers, "dtype": "bf16",
+                          "prefill": {"tokens": PREFILL_TOKENS, "ms": round(r["prefill_ms"], 3),
+                                      "value": round(PREFILL_TOKENS * 1000.0 / r["prefill_ms"], 1)}}))
         return 0
     if a.gpus != 1:
         print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
