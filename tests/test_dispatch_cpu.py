@@ -39,3 +39,22 @@ def test_choices_at_the_benchmark_sizes():
     for f in (13824, 25600):
         kind, _, variant = fast._prefill_tile(2048, 5120, f)
         assert not (kind == "pair" and variant)
+
+
+def test_split_k_plans_of_products_with_a_few_hundred_rows():
+    for m, n, k in itertools.product((129, 200, 256, 384, 511, 512, 700, 1023), (96, 520, 2560, 5120), (64, 520, 2560, 10496, 25600)):
+        plan = fast._prefill_split(m, n, k)
+        if plan is None:
+            continue
+        bn, sp = plan
+        assert bn in (128, 192, 256) and 2 <= sp <= 8
+        assert -(-(-(-k // 64)) // sp) >= 8                  # a split keeps at least 8 K blocks
+        assert -(-m // 128) * -(-n // bn) * sp <= 2 * fast.N_SM
+    assert fast._prefill_split(256, 2560, 10496) is not None and fast._prefill_split(2048, 2560, 10496) is None
+
+
+def test_decode_position_splits():
+    ctx = lambda b: type("Ctx", (), {"B": b})()
+    assert fast.decode_splits(ctx(1), 4) == 64 and fast.decode_splits(ctx(8), 4) == 9
+    assert fast.decode_splits(ctx(32), 4) == 1 and fast.decode_splits(ctx(64), 4) == 1
+    assert fast.decode_splits(ctx(16), 4) == 4 and fast.decode_splits(ctx(1), 1) == 64
