@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from ..parts.base import KVNeed, StateNeed
-from .pages import PAGE, CacheError, CacheFull, FreeList, PageMap, pages_for
+from .pages import PAGE, CacheError, FreeList, PageMap, pages_for
 
 
 @dataclass

@@ -15,7 +15,6 @@ for each, ``:1144-1192``); this one function covers all three for a batch.
 """
 from __future__ import annotations
 
-import os
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch

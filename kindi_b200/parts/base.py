@@ -12,7 +12,7 @@ same way: its fused add + RMS norm at the start of the next sub-layer, ``kindi/n
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+from typing import Any, Dict, Mapping, Optional, Tuple
 
 import torch
 

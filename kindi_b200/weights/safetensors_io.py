@@ -11,7 +11,7 @@ import json
 import mmap
 import os
 import struct
-from typing import Dict, Iterable, List, Mapping, Tuple
+from typing import Dict, List, Mapping, Tuple
 
 import torch
 

@@ -1,6 +1,5 @@
 """Configuration: typed reading of config.json, clear errors, the registries."""
 import json
-import os
 
 import pytest
 

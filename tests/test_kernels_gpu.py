@@ -2,7 +2,6 @@
 engine's: odd widths, tile edges, head sizes in steps of 16, any number of heads and groups."""
 import math
 
-import numpy as np
 import pytest
 import torch
 

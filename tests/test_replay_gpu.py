@@ -1,8 +1,6 @@
 """Replay on the GPU against the plain implementation: each request whole; with its last 32 tokens one by one; in
 batches of unequal lengths whose shorter requests end earlier, one batch after another so that slots and pages are
 used again. In 32-bit and in bfloat16, for every tiny configuration."""
-import os
-
 import numpy as np
 import pytest
 import torch

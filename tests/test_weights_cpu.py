@@ -9,7 +9,7 @@ import torch
 import tiny
 from kindi_b200.config import model_from_config
 from kindi_b200.parts.model import expected_tensors
-from kindi_b200.weights import SafetensorsFile, WeightError, load_tensors, write_file
+from kindi_b200.weights import WeightError, load_tensors, write_file
 from kindi_b200.weights.random_init import write_random_model
 
 
