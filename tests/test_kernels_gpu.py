@@ -534,3 +534,54 @@ def test_attention_window_edge(K, kind, hd, dtype):
     for key in (pos_row - window + 1, pos_row - window):
         err = _run_attention(K, kind, dtype, 4, 2, hd, [ql, 1], [kv, 70], window, seed=hd + key, boost=(0, row, key))
         assert err < tol, (kind, key, err)
+
+
+def test_embedding_scale_and_logit_scale_with_soft_cap(K):
+    """the options of the embedding and head parts: rows times a scale; logits times a scale, then cap * tanh(z / cap)"""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    st = _status()
+    for dtype in (torch.float32, torch.bfloat16):
+        table = torch.randn(53, 40, device="cuda", generator=g).to(dtype)
+        tok = torch.tensor([0, 52, 7, 7, 31], dtype=torch.int32, device="cuda")
+        out = torch.full((5, 40), float("nan"), device="cuda")
+        K.embed(table, tok, out, st, 6.5)
+        assert int(st.item()) == 0 and torch.equal(out, table.float()[tok.long()] * 6.5)
+    z = torch.randn(7, 1001, device="cuda", generator=g) * 9.0
+    for scale, cap in ((0.5, 0.0), (1.0, 4.0), (0.25, 30.0)):
+        got = z.clone()
+        K.logit_post(got, scale, cap)
+        want = z.double() * scale
+        if cap > 0:
+            want = cap * torch.tanh(want / cap)
+        assert _rel(got, want) < 1e-6
+        if cap > 0:
+            assert float(got.abs().max()) <= cap
+
+
+def test_rotation_angles_of_a_step_are_the_kernels_own(K):
+    """the cosines and sines a step computes once (rope_table) give the rotate-and-store kernel the same bits as its own
+    computation, for rows and for 32-bit planes; rows with position -1 are left alone"""
+    g = torch.Generator().manual_seed(11)
+    T, nh, nkv, hd = 70, 5, 1, 128
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, generator=g).to(torch.bfloat16).cuda()
+    pos = torch.arange(1000, 1000 + T, dtype=torch.int32)
+    pos[-3:] = -1
+    inv = (7e7 ** (-2 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().cuda()
+    table = torch.arange(32, dtype=torch.int32)[None].contiguous().cuda()
+    seq = torch.zeros(T, dtype=torch.int32).cuda()
+    slot = torch.zeros(1, dtype=torch.int32).cuda()
+    st = _status()
+    res = []
+    for use_table in (False, True):
+        pool = torch.zeros(32, 2, nkv, 64, hd, dtype=torch.bfloat16, device="cuda")
+        q = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+        ang = K.rope_table(pos.cuda(), inv, hd) if use_table else None
+        K.rope_store(qkv.clone(), q, inv, hd, pos.cuda(), seq, slot, nh, nkv, hd, pool, table, 32, st, ang)
+        assert int(st.item()) == 0
+        res.append((q.clone(), pool.clone()))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    assert bool((res[1][0][-3:] == 7.0).all())                       # padding rows: queries not written
+    first_pad = 1000 + T - 3                                           # the first position that no row stores
+    assert float(res[1][1][first_pad // 64, :, :, first_pad % 64:].abs().sum()) == 0.0
+    assert float(res[1][1][first_pad // 64, :, :, first_pad % 64 - 1].abs().sum()) > 0.0
