@@ -480,3 +480,144 @@ def test_toy_architecture_from_a_model_folder(tmp_path, dtype, tol):
     (tmp_path / "bad" / "config.json").write_text(json.dumps(bad))
     with pytest.raises(ConfigError):
         model_from_dir(str(tmp_path / "bad"))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# another norm and another block arrangement, defined here: a LayerNorm with bias (mean removed, gain and bias) and a
+# block that runs mixer and feed-forward side by side on ONE normalised input (x += mixer(n(x)) + feed_forward(n(x))),
+# around the package's own attention and SwiGLU parts.
+def _toy_norm_and_block():
+    from kindi_b200.config.registry import part_class, register_part
+    from kindi_b200.parts.base import Block, Branch, Norm
+
+    class BiasLayerNorm(Norm):
+        @classmethod
+        def tensor_shapes(cls, spec, width):
+            return {"weight": (width,), "bias": (width,)}
+
+        @classmethod
+        def tensor_init(cls, spec, width):
+            return {"weight": "gain", "bias": "zero"}
+
+        def __init__(self, spec, width, weights, *, dtype, device):
+            super().__init__(spec, width, weights, dtype=dtype, device=device)
+            self.eps = float(spec["eps"])
+            self.w, self.b = weights("weight").float(), weights("bias").float()
+
+        def add_norm(self, ctx, x, pending, rows=None):
+            if pending is not None:
+                v = x + pending.parts.sum(0) if rows is not None else x.add_(pending.parts.sum(0))
+            else:
+                v = x
+            if rows is not None:
+                v = v[rows.long()]
+            mu = v.mean(-1, keepdim=True)
+            var = ((v - mu) ** 2).mean(-1, keepdim=True)
+            return (((v - mu) * torch.rsqrt(var + self.eps)) * self.w + self.b).to(self.dtype)
+
+    class ParallelBlock(Block):
+        @classmethod
+        def _parts(cls, spec):
+            return (("norm", "norm", "ln."), ("mixer", "mixer", "attn."), ("feed_forward", "feed_forward", "ff."))
+
+        @classmethod
+        def tensor_shapes(cls, spec, width):
+            out = {}
+            for role, cat, sub in cls._parts(spec):
+                for sfx, shape in part_class(cat, spec[role].kind).tensor_shapes(spec[role], width).items():
+                    out[sub + sfx] = shape
+            return out
+
+        @classmethod
+        def tensor_init(cls, spec, width):
+            out = {}
+            for role, cat, sub in cls._parts(spec):
+                for sfx, kind in part_class(cat, spec[role].kind).tensor_init(spec[role], width).items():
+                    out[sub + sfx] = kind
+            return out
+
+        @classmethod
+        def cache_need(cls, spec, width):
+            return part_class("mixer", spec["mixer"].kind).cache_need(spec["mixer"], width)
+
+        def __init__(self, spec, width, weights, *, dtype, device):
+            super().__init__(spec, width, weights, dtype=dtype, device=device)
+            self.norm, self.mixer, self.ff = (
+                part_class(cat, spec[role].kind)(spec[role], width, weights.sub(sub), dtype=dtype, device=device)
+                for role, cat, sub in self._parts(spec))
+            self.graph_safe = all(p.graph_safe for p in (self.norm, self.mixer, self.ff))
+
+        def forward(self, ctx, x, pending):
+            y = self.norm.add_norm(ctx, x, pending)
+            a, f = self.mixer.forward(ctx, y), self.ff.forward(ctx, y)
+            return Branch(torch.cat([a.parts, f.parts], dim=0))          # both branches are added by the next norm
+
+    register_part("norm", "toy_bias_layernorm", BiasLayerNorm, replace=True)
+    register_part("block", "toy_parallel", ParallelBlock, replace=True)
+
+
+def _toy_parallel_spec(width=80, vocab=113):
+    from kindi_b200.config.spec import LayerSpec, ModelSpec, PartSpec, default_schedule
+    norm = PartSpec("toy_bias_layernorm", {"eps": 1e-5})
+    att = PartSpec("attention", {"n_heads": 5, "n_kv_heads": 5, "head_dim": 16, "window": None,
+                                 "position": PartSpec("rotary", {"base": 10000.0, "rotary_dim": 16})})
+    ffn = PartSpec("swiglu", {"intermediate": 112})
+    block = PartSpec("toy_parallel", {"norm": norm, "mixer": att, "feed_forward": ffn})
+    return ModelSpec(architecture="toy_parallel", vocab_size=vocab, width=width,
+                     layers=tuple(LayerSpec(block, "blk%d." % i) for i in range(2)), schedule=default_schedule(2),
+                     final_norm=norm, final_norm_prefix="out_ln.",
+                     embedding=PartSpec("table", {"name": "emb", "vocab": vocab}),
+                     head=PartSpec("linear", {"name": "head", "tied_to": "emb", "vocab": vocab}))
+
+
+def _toy_parallel_plain(w, tokens):
+    w = {k: v.double().cpu() for k, v in w.items()}
+    n = len(tokens)
+
+    def ln(v, p):
+        mu = v.mean(-1, keepdim=True)
+        return (v - mu) / torch.sqrt(((v - mu) ** 2).mean(-1, keepdim=True) + 1e-5) * w[p + "weight"] + w[p + "bias"]
+    x = P.embedding(w["emb"], tokens)
+    cos, sin = P.rope_tables(torch.arange(n), 16, 10000.0, torch.float64)
+    for i in range(2):
+        p = "blk%d." % i
+        y = ln(x, p + "ln.")
+        q = P.rope_rotate_half((y @ w[p + "attn.q_proj.weight"].T).view(n, 5, 16), cos, sin)
+        k = P.rope_rotate_half((y @ w[p + "attn.k_proj.weight"].T).view(n, 5, 16), cos, sin)
+        v = (y @ w[p + "attn.v_proj.weight"].T).view(n, 5, 16)
+        a = P.attention(q, k, v, 0.25).reshape(n, 80) @ w[p + "attn.o_proj.weight"].T
+        f = P.swiglu_mlp(y, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+        x = x + a + f
+    return ln(x, "out_ln.") @ w["emb"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 1.5e-2)])
+def test_toy_norm_and_parallel_block(tmp_path, dtype, tol):
+    """a norm with a bias and a block that runs attention and feed-forward side by side, both defined in this file: the
+    engine, the cache (five key/value heads of size 16), the decode recordings and the replay modes take them as
+    they are"""
+    from kindi_b200.engine.engine import Engine
+    from kindi_b200.parts.model import expected_tensors, tensor_inits
+    from kindi_b200.weights.random_init import random_tensors
+    _toy_norm_and_block()
+    spec = _toy_parallel_spec()
+    shapes = expected_tensors(spec)
+    assert shapes["blk1.ln.bias"] == (80,) and tensor_inits(spec)["blk0.ln.bias"] == "zero"
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = random_tensors(shapes, seed=21, std=0.05, dtype=tdt, inits=tensor_inits(spec))
+    for n in list(w):
+        if n.endswith(".bias"):
+            w[n] = (torch.randn(w[n].shape, generator=torch.Generator().manual_seed(len(n))) * 0.1).to(tdt)
+    eng = Engine(spec=spec, tensors=w, ctx=1024, dtype=dtype, max_batch=3)
+    reqs = tiny.random_requests(113, [50, 9, 77, 2], seed=6)
+    want = {r: _toy_parallel_plain(w, t).numpy() for r, t in reqs.items()}
+    for steps in (tiny.trace_whole(reqs), tiny.trace_last_n(reqs, 32), tiny.trace_batched(reqs, batch=3, decode=10)):
+        out = str(tmp_path / ("p%d" % len(steps)))
+        tiny.run_replay(eng, steps, out)
+        got = tiny.collect(out, steps, 113)
+        for r, t in reqs.items():
+            mine = np.stack([got[(r, i)] for i in range(len(t))])
+            assert tiny.rel_err(mine, want[r]) < tol, (len(steps), r, tiny.rel_err(mine, want[r]))
+        eng.cache.check()
+    if eng.cuda_graphs:
+        assert eng.graph_replays > 0
