@@ -2,8 +2,9 @@
 
 ``step`` takes a batch of sequences, each with its next tokens (a whole prompt, or one token, or any run in
 between) and the places whose logits are wanted. It runs only those tokens, as one packed batch, against the cache
-that earlier steps left, stores their keys and values, and returns 32-bit logits at the wanted places. There is
-no padding, so no result can depend on it. In float32 a row's logits do not depend on what else is in the batch or
+that earlier steps left, stores their keys and values, and returns 32-bit logits at the wanted places. Sequences
+are never padded to one another's length (the only padding are whole rows at the end of a recorded short prompt
+step, which belong to no sequence and store nothing), so no result depends on padding. In float32 a row's logits do not depend on what else is in the batch or
 on how the tokens were cut into steps, bit for bit: every sum is taken in an order that depends on positions only.
 In bfloat16 they agree up to rounding: the serving kernels choose tile widths and the number of ways a product or a
 sequence's keys are split from the step's row count, so the last bits - and with them a greedy token at a near tie -
