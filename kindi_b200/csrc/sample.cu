@@ -25,14 +25,42 @@ __device__ __forceinline__ unsigned long long sm_fix(float w) { return (unsigned
 __device__ void sm_argmax(const float* z, int V, float* s_v, int* s_i, float& best, int& best_i) {
     float v = -INFINITY;
     int idx = 0x7fffffff;
-    // four strided loads in flight per thread; within a thread indices rise, so ">" keeps the lowest index of a tie
-    int i = threadIdx.x;
-    for (; i + 3 * SM_THREADS < V; i += 4 * SM_THREADS) {
-        const float x0 = z[i], x1 = z[i + SM_THREADS], x2 = z[i + 2 * SM_THREADS], x3 = z[i + 3 * SM_THREADS];
-        if (x0 > v || idx == 0x7fffffff) { v = x0; idx = i; }
-        if (x1 > v) { v = x1; idx = i + SM_THREADS; }
-        if (x2 > v) { v = x2; idx = i + 2 * SM_THREADS; }
-        if (x3 > v) { v = x3; idx = i + 3 * SM_THREADS; }
+    // within a thread indices rise, so ">" keeps the lowest index of a tie
+    int i;
+    if ((((uintptr_t)z) & 15) == 0) {
+        // four neighbouring logits per load, four loads in flight per thread
+        const float4* z4 = (const float4*)z;
+        const int n4 = V >> 2;
+        int j = threadIdx.x;
+#define SM_TAKE4(q, base)                                                        \
+        do {                                                                     \
+            if (q.x > v || idx == 0x7fffffff) { v = q.x; idx = (base); }         \
+            if (q.y > v) { v = q.y; idx = (base) + 1; }                          \
+            if (q.z > v) { v = q.z; idx = (base) + 2; }                          \
+            if (q.w > v) { v = q.w; idx = (base) + 3; }                          \
+        } while (0)
+        for (; j + 3 * SM_THREADS < n4; j += 4 * SM_THREADS) {
+            const float4 q0 = z4[j], q1 = z4[j + SM_THREADS], q2 = z4[j + 2 * SM_THREADS], q3 = z4[j + 3 * SM_THREADS];
+            SM_TAKE4(q0, 4 * j);
+            SM_TAKE4(q1, 4 * (j + SM_THREADS));
+            SM_TAKE4(q2, 4 * (j + 2 * SM_THREADS));
+            SM_TAKE4(q3, 4 * (j + 3 * SM_THREADS));
+        }
+        for (; j < n4; j += SM_THREADS) {
+            const float4 q0 = z4[j];
+            SM_TAKE4(q0, 4 * j);
+        }
+#undef SM_TAKE4
+        i = 4 * n4 + threadIdx.x;                       // the last V % 4 logits
+    } else {
+        i = threadIdx.x;
+        for (; i + 3 * SM_THREADS < V; i += 4 * SM_THREADS) {
+            const float x0 = z[i], x1 = z[i + SM_THREADS], x2 = z[i + 2 * SM_THREADS], x3 = z[i + 3 * SM_THREADS];
+            if (x0 > v || idx == 0x7fffffff) { v = x0; idx = i; }
+            if (x1 > v) { v = x1; idx = i + SM_THREADS; }
+            if (x2 > v) { v = x2; idx = i + 2 * SM_THREADS; }
+            if (x3 > v) { v = x3; idx = i + 3 * SM_THREADS; }
+        }
     }
     for (; i < V; i += SM_THREADS) {
         float x = z[i];
