@@ -224,3 +224,20 @@ def test_cancel_with_a_step_under_way():
         return len(calls) >= 3
     res = generate(st, [[1, 2, 3], [4]], SamplingParams(temperature=0.0, max_tokens=50), cancel=cancel)
     assert res.finish == ["stop", "stop"] and len(res.tokens[0]) == 3 and not st.held and st.in_flight == 0
+
+
+def test_pack_with_padding_rows():
+    """a recorded prompt step is padded to a fixed number of rows: the padding rows carry token 0 and position -1, lie
+    behind every sequence's row range, and the sequences' own numbers are what they are without padding"""
+    entries = [StepEntry(3, (5, 6, 7), (2,)), StepEntry(1, (9,) * 10, (9,))]
+    plain = pack(entries, [4, 0])
+    padded = pack(entries, [4, 0], pad_rows_to=64)
+    assert (plain.T, padded.T, padded.B, padded.R) == (13, 64, 2, 2) and not padded.decode
+    seg = lambda ps, n: ps.meta[ps.off[n][0]: ps.off[n][0] + ps.off[n][1]].tolist()
+    assert seg(padded, "tok")[:13] == seg(plain, "tok") and set(seg(padded, "tok")[13:]) == {0}
+    assert seg(padded, "pos")[:13] == [4, 5, 6] + list(range(10)) and set(seg(padded, "pos")[13:]) == {-1}
+    assert set(seg(padded, "seq")[13:]) == {0}
+    for name in ("slot", "q_start", "kv_len", "rows"):
+        assert seg(padded, name) == seg(plain, name)
+    assert padded.h_kv_len == plain.h_kv_len == (7, 10) and padded.max_q == 10
+    assert pack(entries, [4, 0], pad_rows_to=8).T == 13            # never fewer rows than tokens

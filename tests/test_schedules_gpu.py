@@ -328,3 +328,26 @@ def test_short_prompt_steps_are_recorded_and_padding_changes_nothing(tmp_path, d
     assert ("prompt", 128, 1, 0) in eng._graphs
     eng.cache.check()
     assert eng.cache.slots.n_held == 0
+
+
+def test_recorded_prompt_shapes_are_kept_up_to_a_limit(tmp_path):
+    """only so many recorded prompt shapes are kept (each holds buffers of its own): the oldest makes room, and a shape
+    that was dropped is recorded again when it comes back"""
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.engine.engine import Engine
+    cfg = tiny.TINY["D"][0]
+    folder = tiny.make_model(tmp_path, "D", "bfloat16")
+    m = P.load_model(folder)
+    eng = Engine(folder, ctx=2048, dtype="bfloat16", max_batch=2)
+    eng.prompt_graphs_kept = 2
+    rng = random.Random(3)
+    for n in (50, 60, 100, 110, 150, 160, 40, 45, 130, 170, 55):
+        toks = [rng.randrange(cfg["vocab_size"]) for _ in range(n)]
+        s = eng.alloc()
+        lg = eng.step([StepEntry(s, tuple(toks), (n - 1,))])[0].cpu().numpy()
+        eng.check_status()
+        eng.free(s)
+        assert tiny.rel_err(lg, P.forward(m, toks).numpy()[-1]) <= TOL["bfloat16"], n
+        assert sum(1 for k in eng._graphs if k[0] == "prompt") <= 2
+    assert ("prompt", 64, 1, 1) in eng._graphs and ("prompt", 192, 1, 1) in eng._graphs
+    assert ("prompt", 128, 1, 1) not in eng._graphs
