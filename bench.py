@@ -572,6 +572,12 @@ def main(argv=None) -> int:
                     "frac": round(by / ms / 1e6 / pk["hbm_gbs"], 4)}
                 if c == a.context and b in point_batches:
                     pts["decode_b%d" % b] = round(b * 1000.0 / ms, 1)
+        for b in (16, 32):                                         # batch sizes between the named points
+            if b != a.batch and b <= max_b and b * (a.context + 2 * a.steps + 64) <= cache_room:
+                ms, _, _, by = bench_decode(eng, b, a.context, max(16, a.steps // 2), a.warmup, False)
+                detail["decode_b%d_ctx%d" % (b, a.context)] = {
+                    "tokens_per_s": round(b * 1000.0 / ms, 1), "ms": round(ms, 4), "bytes_per_step": int(by),
+                    "frac": round(by / ms / 1e6 / pk["hbm_gbs"], 4)}
         out["points"] = pts
         out["points_detail"] = detail
         out["kernels"] = kernel_times(eng, a.batch, a.context, PREFILL_TOKENS)

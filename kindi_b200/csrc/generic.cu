@@ -791,6 +791,13 @@ extern "C" int kb_rope_table(const int* pos, const float* inv_freq, int rot, int
 
 // in: [n_planes][T][ld_in] (the planes are summed in order); in_dtype may be 32-bit planes with a bf16 cache / qout
 // cs_table (may be null): float2 [T][rot / 2] made by kb_rope_table for these rows; used where the kernel form takes it
+// Fewer rows than this (decode steps) go through the small blocks of k_rope_store: a row-wise block with planes holds
+// most of an SM's registers, and the few SMs that such blocks occupy are closed to the CTAs of the attention kernel
+// that is launched beside them (32 sequences at context 8192: 4.97 -> 4.66 ms a step; 64: 7.39 -> 7.32).
+#define KB_ROPE_ROW_MIN_T 96
+// the fewest rows for which kb_rope_store reads a table of the step's cosines and sines (kb_rope_table)
+extern "C" int kb_rope_table_min_rows() { return KB_ROPE_ROW_MIN_T; }
+
 extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in,
                              void* qout, int dtype, int ldq, const float* inv_freq, int rot, const int* pos,
                              const int* seq, const int* slot, int T, int nh, int nkv, int hd, void* pool,
@@ -801,7 +808,7 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
     dim3 grid(T, nh + 2 * nkv);
     int thr = hd / 2 < 32 ? 32 : (hd / 2 > 128 ? 128 : ((hd / 2 + 31) / 32) * 32);
     const int in_el = in_dtype == KB_F32 ? 4 : 2, out_el = dtype == KB_F32 ? 4 : 2;
-    const bool by_row = T >= 32 && rot % 4 == 0 && hd % 2 == 0 && ld_in % 2 == 0 && ldq % 2 == 0 && plane_stride % 2 == 0 &&
+    const bool by_row = T >= KB_ROPE_ROW_MIN_T && rot % 4 == 0 && hd % 2 == 0 && ld_in % 2 == 0 && ldq % 2 == 0 && plane_stride % 2 == 0 &&
                         ((uintptr_t)in % (2 * in_el)) == 0 && ((uintptr_t)qout % (2 * out_el)) == 0 &&
                         ((uintptr_t)pool % (2 * out_el)) == 0 && rot / 2 * 8 <= 32 * 1024;
     const bool by_row8 = by_row && rot % 16 == 0 && hd % 8 == 0 && ld_in % 8 == 0 && ldq % 8 == 0 &&

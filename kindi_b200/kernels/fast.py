@@ -252,6 +252,12 @@ def attention_decode_rope(ctx, qkv, out, nh, nkv, hd, scale, window, inv_freq, r
     if qkv.stride(2) != 1 or qkv.stride(1) != qkv.shape[2] or qkv.shape[2] % 2 or qkv.stride(0) % 2 \
             or qkv.data_ptr() % 8 or out.stride(0) % 2:
         return False
+    splits = decode_splits(ctx, nkv)
+    if splits == 1:
+        # one CTA per (sequence, key/value head): nothing runs beside a CTA's sums and rotation, and the step is
+        # slower than with the rotate-and-store kernel in front (25 / 28 / 31 sequences x 4 heads at context 8192:
+        # 4.54 / 4.59 / 4.67 ms against 4.33 / 4.44 / 4.58)
+        return False
     K.attn_decode_rope(qkv, inv_freq, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool,
-                       store, table, n_pages, grid_x=decode_splits(ctx, nkv), status=ctx.status)
+                       store, table, n_pages, grid_x=splits, status=ctx.status)
     return True

@@ -45,6 +45,7 @@ _SIGS = {
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_longlong, c_void_p, c_void_p, c_int, c_int],
     "kb_gemm_tc_splits": [c_int, c_int],
+    "kb_rope_table_min_rows": [],
     "kb_gemm_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                      c_void_p, c_int, c_void_p, c_void_p],
     "kb_gemm_swiglu_decode": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -103,7 +104,7 @@ class KernelTiming:
 
     def __getattr__(self, name):                       # stands in for the library while timing is on
         fn = getattr(_lib, name)
-        if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits"):
+        if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits", "kb_rope_table_min_rows"):
             return fn
 
         def timed(*args):
@@ -266,6 +267,12 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     _check(load().kb_gemm_simt(_p(a), dt(a), _p(w), dt(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0),
                                out.stride(0), _stream()), "gemm_simt")
+
+
+@functools.lru_cache(maxsize=1)
+def rope_table_min_rows() -> int:
+    """steps of fewer rows are rotated by kernels that compute their angles themselves and read no table"""
+    return load().kb_rope_table_min_rows()
 
 
 def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, rot: int) -> torch.Tensor:

@@ -30,7 +30,7 @@ class RotationEncoding(PositionEncoding):
 
     def encode_and_store(self, ctx, qkv, q_out, n_heads, n_kv_store, head_dim, pool, table, n_pages) -> None:
         angles = None
-        if self.angles_key is not None and ctx.T >= 32 and self.rotary_dim >= 16:
+        if self.angles_key is not None and ctx.T >= K.rope_table_min_rows() and self.rotary_dim >= 16:
             angles = ctx.scratch.get(self.angles_key)
             if angles is None:
                 angles = ctx.scratch[self.angles_key] = K.rope_table(ctx.pos, self.inv_freq, self.rotary_dim)

@@ -473,7 +473,9 @@ def test_swiglu(K, T, F, group, planes):
 
 
 @pytest.mark.parametrize("T,nh,nkv,hd,rot,planes", [(5, 3, 1, 48, 32, 0), (40, 20, 4, 128, 128, 0), (8, 20, 4, 128, 128, 5),
-                                                    (33, 2, 2, 18, 6, 0), (64, 5, 1, 64, 32, 3), (36, 3, 1, 24, 12, 0)])
+                                                    (33, 2, 2, 18, 6, 0), (64, 5, 1, 64, 32, 3), (36, 3, 1, 24, 12, 0),
+                                                    (100, 20, 4, 128, 128, 0), (130, 5, 1, 64, 32, 3),
+                                                    (97, 3, 1, 24, 12, 0), (150, 2, 2, 18, 6, 0)])
 def test_rope_store_against_plain(K, T, nh, nkv, hd, rot, planes):
     """rotation of q in place or from planes, keys rotated into the cache pages, values copied; both kernels
     (one block per head for small steps, one block per row for larger ones) against the same formulas"""
@@ -489,12 +491,13 @@ def test_rope_store_against_plain(K, T, nh, nkv, hd, rot, planes):
     def rot_ref(x):                      # [T, heads, hd]
         a, b, rest = x[..., : rot // 2], x[..., rot // 2: rot], x[..., rot:]
         return torch.cat([a * cos[:, None] - b * sin[:, None], b * cos[:, None] + a * sin[:, None], rest], -1)
-    q_ref = rot_ref(qkv[:, : nh * hd].double().view(T, nh, hd))
-    k_ref = rot_ref(qkv[:, nh * hd: (nh + nkv) * hd].double().view(T, nkv, hd))
-    v_ref = qkv[:, (nh + nkv) * hd:].double().view(T, nkv, hd)
     n_pages = 4
-    table = torch.tensor([[2, 0, 3, 1]], dtype=torch.int32).cuda()          # positions 100.. lie in blocks 1 and 2
+    table = torch.tensor([[2, 0, 3, 1]], dtype=torch.int32).cuda()          # positions 100.. lie in blocks 1 to 3
     for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 6e-3)):
+        given = qkv if planes else qkv.to(dtype).float()                    # what the kernel is handed
+        q_ref = rot_ref(given[:, : nh * hd].double().view(T, nh, hd))
+        k_ref = rot_ref(given[:, nh * hd: (nh + nkv) * hd].double().view(T, nkv, hd))
+        v_ref = given[:, (nh + nkv) * hd:].double().view(T, nkv, hd)
         pool = torch.zeros(n_pages, 2, nkv, 64, hd, dtype=dtype, device="cuda")
         st = _status()
         seq = torch.zeros(T, dtype=torch.int32).cuda()
@@ -562,7 +565,7 @@ def test_rotation_angles_of_a_step_are_the_kernels_own(K):
     """the cosines and sines a step computes once (rope_table) give the rotate-and-store kernel the same bits as its own
     computation, for rows and for 32-bit planes; rows with position -1 are left alone"""
     g = torch.Generator().manual_seed(11)
-    T, nh, nkv, hd = 70, 5, 1, 128
+    T, nh, nkv, hd = 134, 5, 1, 128
     width = (nh + 2 * nkv) * hd
     qkv = torch.randn(T, width, generator=g).to(torch.bfloat16).cuda()
     pos = torch.arange(1000, 1000 + T, dtype=torch.int32)
