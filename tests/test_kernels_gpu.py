@@ -192,6 +192,30 @@ def test_attention_mma_decode(K, nh, nkv, hd, window):
     assert err < 1e-2
 
 
+def test_attention_mma_decode_with_a_cta_alone_on_its_sm(K):
+    """a decode step of no more CTAs than SMs (one split, 30 sequences x 4 heads) asks for an SM per CTA: the same
+    results as with any other launch shape"""
+    kv_lens = [1 + (37 * i) % 700 for i in range(30)]
+    pool, table, dense, slots, n_pages = _make_cache(kv_lens, 4, 128, torch.bfloat16, seed=5)
+    g = torch.Generator(device="cpu").manual_seed(6)
+    B, nh, nkv, hd = len(kv_lens), 20, 4, 128
+    q = torch.randn(B, nh, hd, generator=g).to(torch.bfloat16)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()      # noqa: E731
+    st = _status()
+    outs = []
+    for splits in (1, 2):
+        out = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        K.attn_mma(q.reshape(B, nh * hd).cuda(), out, slots, dev(list(range(B + 1))), dev(kv_lens), B, nh, nkv, hd,
+                   1.0 / math.sqrt(hd), 0, pool, table, n_pages, decode=True, grid_x=splits, status=st)
+        assert int(st.item()) == 0
+        outs.append(out.float().cpu().reshape(B, nh, hd))
+    for b in range(B):
+        ref = _attn_ref(q[b:b + 1].float(), dense[b][0].float(), dense[b][1].float(), [kv_lens[b] - 1],
+                        1.0 / math.sqrt(hd), 0)
+        for o in outs:
+            assert float((o[b:b + 1].double() - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
 @pytest.mark.parametrize("nh,nkv,hd,window,planes", [(20, 4, 128, 0, 5), (3, 1, 64, 0, 1), (16, 1, 128, 0, 2),
                                                      (14, 2, 64, 100, 7), (10, 2, 128, 64, 3)])
 def test_attention_decode_rotates_and_stores_by_itself(K, nh, nkv, hd, window, planes):
