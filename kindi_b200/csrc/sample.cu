@@ -15,8 +15,10 @@
 #define SM_THREADS 1024
 #define SM_FIX 1099511627776.0          // 2^40: weights in (0, 1] as fixed point
 
+// a logit as an unsigned key of the same order; -0 and +0, equal as numbers, get the same key
 __device__ __forceinline__ unsigned sm_key(float f) {
     unsigned u = __float_as_uint(f);
+    if (u == 0x80000000u) u = 0u;
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 __device__ __forceinline__ unsigned long long sm_fix(float w) { return (unsigned long long)((double)w * SM_FIX); }

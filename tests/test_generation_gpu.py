@@ -112,6 +112,19 @@ def test_sampling_kernel_against_the_plain_sampler(opts):
             assert got[r] == _plain_pick(z[r].astype(np.float64), us[r], params, hist[r]), (V, r, opts)
 
 
+def test_sampling_kernel_takes_minus_zero_for_zero():
+    """logits of -0 and +0 are one value: a cut that falls on a zero keeps both (rounded logits, so ties abound)"""
+    from kindi_b200.config.runtime import SamplingParams
+    from kindi_b200.sampling.sampler import Sampler
+    params = SamplingParams(temperature=1.5, top_p=0.95, top_k=7, min_p=0.2, order="hf")
+    z = np.array([-0.0, 0.5, 0.0, -0.75, 2.0 / 3, -0.75, 0.75, 0.0, 0.0, -0.5, -0.75, 0.25, -0.0, 0.75, 0.0, -1.0, 0.0],
+                 dtype=np.float32)
+    us = [0.0, 0.06, 0.2, 0.5, 0.74, 0.9, 0.999]
+    got = Sampler("cuda").pick(torch.from_numpy(np.tile(z, (len(us), 1))).cuda(), params, us, [[]] * len(us)).tolist()
+    want = [_plain_pick(z.astype(np.float64), u, params) for u in us]
+    assert got == want and want[0] == 0 and 12 in want
+
+
 def test_sampled_tokens_do_not_depend_on_the_batch(tmp_path):
     from kindi_b200 import Engine
     d = tiny.make_model(tmp_path, "B", "float32")
