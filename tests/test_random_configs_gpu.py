@@ -6,7 +6,9 @@ layers, eps, rope base, tied or not, windows on some layers), a dtype, a set of 
 into steps: whole, the last tokens one by one, batches that shrink, groups that decode for unequal numbers of steps,
 or one request in portions of any size. The engine is given random limits too (the longest step, the longest
 recorded prompt step). Every wanted row of logits is compared with the plain model's row of the whole sequence.
-The wide cases run 24 to 48 sequences a step, where a decode step takes other kernels than below 25.
+The wide cases run 24 to 48 sequences a step, where a decode step takes other kernels than below 25. The odd cases
+draw sizes no kernel is tuned for: head sizes in steps of 8 and some that are no multiple of 8 (2 to 250), widths
+like 33 and 101, a feed-forward of 8 or 333, a vocabulary of 3.
 """
 from __future__ import annotations
 
@@ -24,7 +26,7 @@ TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
 LENGTHS = [1, 2, 5, 33, 64, 65, 100, 129, 200, 290]
 
 
-def _draw_config(rng: random.Random, wide: bool) -> dict:
+def _draw_config(rng: random.Random, wide: bool, odd: bool = False) -> dict:
     if wide:
         hd, nkv, g = rng.choice([32, 64, 128, 128]), rng.choice([1, 2, 3, 4]), rng.choice([1, 2, 5])
     else:
@@ -36,6 +38,10 @@ def _draw_config(rng: random.Random, wide: bool) -> dict:
                num_hidden_layers=layers, num_attention_heads=nkv * g, num_key_value_heads=nkv, head_dim=hd,
                rms_norm_eps=rng.choice([1e-5, 1e-6, 3e-6]), rope_theta=rng.choice([1e4, 5e5, 7e7]),
                tie_word_embeddings=rng.random() < 0.5)
+    if odd:
+        cfg.update(head_dim=rng.choice(list(range(8, 264, 8)) + [12, 20, 36, 2, 6, 250]),
+                   hidden_size=rng.choice([62, 70, 101, 64, 136, 264, 33]),
+                   intermediate_size=rng.choice([97, 150, 333, 64, 8, 1000]), vocab_size=rng.choice([3, 17, 127, 1001, 257]))
     window = rng.choice([None, None, 33, 70, 130])
     if window:
         cfg["sliding_window"] = window
@@ -61,13 +67,13 @@ def _portions(eng, reqs, want, rng):
     return worst
 
 
-@pytest.mark.parametrize("case", list(range(16)) + [1000 + i for i in range(8)])
+@pytest.mark.parametrize("case", list(range(16)) + [1000 + i for i in range(8)] + [2000 + i for i in range(12)])
 def test_random_configuration_and_schedule(tmp_path, case):
     from kindi_b200.engine.engine import Engine
     from kindi_b200.weights.random_init import write_random_model
     rng = random.Random(case)
-    wide = case >= 1000
-    cfg = _draw_config(rng, wide)
+    wide = 1000 <= case < 2000
+    cfg = _draw_config(rng, wide, odd=case >= 2000)
     dtype = rng.choice(["float32", "bfloat16"])
     folder = write_random_model(str(tmp_path / "m"), cfg, case, dtype=dtype)
     model = P.load_model(folder)
