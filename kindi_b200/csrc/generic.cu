@@ -309,6 +309,90 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* __restrict__
     }
 }
 
+// Four warps per row, each with a quarter of the row in registers (widths up to 4 * NC * 128), and the planes taken
+// several at a time: a step of a few hundred rows has too few rows to hide the round trips of one warp per row
+// behind other rows (a row of 2560 with six planes: 18 trips for one warp, 4 here). The planes are added in order;
+// the four warps' sums of squares are added in warp order.
+template <typename TW, int NC>
+__global__ void __launch_bounds__(256, 2) k_add_rmsnorm_row4(float* __restrict__ x, const float* __restrict__ delta,
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
+    constexpr int PB = 12 / NC > 0 ? 12 / NC : 1;          // planes in flight
+    __shared__ float s_ss[8];
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, part = warp & 3;
+    const int t = blockIdx.x * 2 + (warp >> 2);
+    const bool live = t < T;
+    float* xr = x + (size_t)t * E;
+    const float* dr = delta + (size_t)t * E;
+    float4 v[NC];
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const int i = ((part * NC + c) * 32 + lane) * 4;
+        v[c] = (live && i < E) ? *(const float4*)(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int s0 = 0; s0 < n_delta; s0 += PB) {
+        float4 d[PB][NC];
+#pragma unroll
+        for (int k = 0; k < PB; k++)
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                const int i = ((part * NC + c) * 32 + lane) * 4;
+                d[k][c] = (live && s0 + k < n_delta && i < E) ? *(const float4*)(dr + (size_t)(s0 + k) * delta_stride + i)
+                                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+        for (int k = 0; k < PB; k++)
+            if (s0 + k < n_delta) {
+#pragma unroll
+                for (int c = 0; c < NC; c++) {
+                    v[c].x += d[k][c].x;
+                    v[c].y += d[k][c].y;
+                    v[c].z += d[k][c].z;
+                    v[c].w += d[k][c].w;
+                }
+            }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const int i = ((part * NC + c) * 32 + lane) * 4;
+        if (live && i < E) {
+            if (n_delta > 0) *(float4*)(xr + i) = v[c];
+            ss = fmaf(v[c].x, v[c].x, ss);
+            ss = fmaf(v[c].y, v[c].y, ss);
+            ss = fmaf(v[c].z, v[c].z, ss);
+            ss = fmaf(v[c].w, v[c].w, ss);
+        }
+    }
+    ss = kb_warp_sum(ss);
+    if (lane == 0) s_ss[warp] = ss;
+    __syncthreads();
+    if (!live) return;
+    const float* q = s_ss + (warp & ~3);
+    const float scale = rsqrtf((((q[0] + q[1]) + q[2]) + q[3]) / (float)E + eps);
+    bf16* yr = y + (size_t)t * E;
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const int i = ((part * NC + c) * 32 + lane) * 4;
+        if (i < E) {
+            const float w0 = kb_to_f<TW>(w[i]), w1 = kb_to_f<TW>(w[i + 1]), w2 = kb_to_f<TW>(w[i + 2]),
+                        w3 = kb_to_f<TW>(w[i + 3]);
+            __nv_bfloat162 a = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(scale, v[c].x), w0),
+                                                     __fmul_rn(__fmul_rn(scale, v[c].y), w1));
+            __nv_bfloat162 b = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(scale, v[c].z), w2),
+                                                     __fmul_rn(__fmul_rn(scale, v[c].w), w3));
+            *(uint2*)(yr + i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+        }
+    }
+}
+
+// Rows of a step for which four warps share a row. Below, a block per row is as fast or faster (128 rows of 2560
+// with one plane: 2.6 against 3.6 us; 160: 4.2 against 3.7); beyond, one warp a row has rows enough to hide its
+// round trips behind (one plane: 512 rows 9.7 against 4.0 us, 1024: 10.8 / 7.0, 1536: 11.9 / 10.0, 2000: 11.8 / 12.7).
+#define NORM_ROW4_MIN_T 160
+#define NORM_ROW4_MAX_T 1792
+
 extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long long delta_stride, const void* w,
                               int wdtype, float eps, void* y, int ydtype, const int* rows, int n_out, int T, int E,
                               int write_back, int* status, cudaStream_t st) {
@@ -318,6 +402,24 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
     const bool vec = (E % 4 == 0) && (((uintptr_t)x) % 16 == 0) && (((uintptr_t)delta) % 16 == 0) &&
                      (delta_stride % 4 == 0);
     cudaError_t e = cudaSuccess;
+    if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= NORM_ROW4_MIN_T && T < NORM_ROW4_MAX_T &&
+        (write_back || n_delta == 0) && (((uintptr_t)y) % 8) == 0 && E <= 4 * 10 * 128) {
+#define KB_NORM_ROW4(NC)                                                                                           \
+    do {                                                                                                           \
+        if (wdtype == KB_F32)                                                                                      \
+            e = kb_launch(k_add_rmsnorm_row4<float, NC>, (T + 1) / 2, 256, 0, st, x, delta, n_delta,               \
+                          (size_t)delta_stride, (const float*)w, eps, (bf16*)y, T, E);                             \
+        else                                                                                                       \
+            e = kb_launch(k_add_rmsnorm_row4<bf16, NC>, (T + 1) / 2, 256, 0, st, x, delta, n_delta,                \
+                          (size_t)delta_stride, (const bf16*)w, eps, (bf16*)y, T, E);                              \
+        return (int)e;                                                                                             \
+    } while (0)
+        if (E <= 4 * 2 * 128) KB_NORM_ROW4(2);
+        if (E <= 4 * 4 * 128) KB_NORM_ROW4(4);
+        if (E <= 4 * 6 * 128) KB_NORM_ROW4(6);
+        KB_NORM_ROW4(10);
+#undef KB_NORM_ROW4
+    }
     if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= 512 && (write_back || n_delta == 0) &&
         (((uintptr_t)y) % 8) == 0) {
 // rows (warps) per block (1, 2 and 4 were measured slower on a 2048-row step)

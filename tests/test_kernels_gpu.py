@@ -450,7 +450,9 @@ def test_decode_gate_up_product_finishes_swiglu_itself(K, M, F, K_):
 
 # ------------------------------------------------------------------------------------------------ small kernels
 @pytest.mark.parametrize("T,E,planes", [(3, 50, 0), (8, 2560, 7), (5, 72, 3), (600, 2560, 1), (600, 96, 9), (70, 4100, 2),
-                                        (520, 1000, 2), (513, 2048, 0), (600, 3200, 1)])
+                                        (520, 1000, 2), (513, 2048, 0), (600, 3200, 1), (601, 5120, 6), (701, 2560, 6),
+                                        (2100, 2560, 3), (2049, 520, 1), (515, 5200, 2), (161, 2560, 7), (159, 2560, 7), (1791, 1024, 1),
+                                        (1793, 1024, 2)])
 @pytest.mark.parametrize("ydtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(K, T, E, planes, ydtype):
     g = torch.Generator(device="cuda").manual_seed(T + E)
