@@ -12,6 +12,11 @@ from . import lib as K
 from .device import DEVICE as DEV
 
 N_SM = DEV.n_sm            # the device's own count (148 on a B200)
+# A TMA tensor whose whole extent (rows x row stride) is below 128 KB is read more slowly when it is the 128-row side of
+# a product: gate/up of 2560 x 20992 in the prompt form takes 28.5 us with 25 activation rows (125 KB) and 22.8 us
+# with 26 (130 KB), and 22.7 us with 8 rows that lie 32 KB apart. (Found by a sweep over the row count; the decode
+# forms, where the activations are the narrow side, show no such step.)
+TMA_SMALL_EXTENT = 128 * 1024
 SMALL_M = 128              # up to here the weights go through the 128-row side of the MMA ("swap" form)
 # prompt-form products of fewer rows may split K into planes (_prefill_split): the down product of 1024 rows takes
 # 51.7 us in six planes and 59.9 us in one; from 1280 rows on the plan finds nothing better than one plane
@@ -181,10 +186,18 @@ def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor
     """out (bf16 [M, F]) = silu(g) * u for a prompt-sized step, finished inside the product's epilogue; w_grouped
     [2F, K] holds 16 gate rows then the 16 up rows of the same outputs, group after group. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
-    if m <= 32 or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
-        return False        # (up to 32 rows the decode form with SwiGLU inside is the faster one)
+    if _swiglu_in_decode_form(a) or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
+        return False
     _prefill_product(a, w_grouped, out, status, True)
     return True
+
+
+def _swiglu_in_decode_form(a: torch.Tensor) -> bool:
+    """which of the two gate/up products that finish SwiGLU themselves takes a step of up to 128 rows: the decode form
+    up to 16 rows (21.6 against 22.7 us at 8 rows), and as long as the activations are a small tensor for the TMA (17
+    to 25 rows of 2560: 23.6-24.8 against 27.5-28.5 us); else the prompt form (26 to 32 rows: 22.8 against 25.1-25.7)"""
+    m = a.shape[0]
+    return m <= 16 or (m <= SMALL_M and m * a.stride(0) * a.element_size() < TMA_SMALL_EXTENT)
 
 
 _SK_SCRATCH = {}           # (device, tiles, bn) -> (partial tiles, flags): scratch of the decode gate/up product
@@ -201,8 +214,9 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
     """out (bf16 [M, F]) = silu(g) * u for a decode-sized step, finished inside the product (no split-K planes, no
     SwiGLU kernel); w_grouped [2F, K] as for gemm_swiglu_rows. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
-    if m > 32 or not _tc_ok(a, w_grouped) or n % 32 or out.stride(1) != 1 or out.dtype != torch.bfloat16:
-        return False        # (from 33 rows on it is level with the split-K product followed by the SwiGLU kernel)
+    if not _swiglu_in_decode_form(a) or not _tc_ok(a, w_grouped) or n % 32 or out.stride(1) != 1 \
+            or out.dtype != torch.bfloat16:
+        return False
     bn = _swap_bn(m)
     tiles = -(-n // 128)
     key = (a.device, tiles, bn)

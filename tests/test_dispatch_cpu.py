@@ -58,3 +58,16 @@ def test_decode_position_splits():
     assert fast.decode_splits(ctx(1), 4) == 64 and fast.decode_splits(ctx(8), 4) == 9
     assert fast.decode_splits(ctx(32), 4) == 1 and fast.decode_splits(ctx(64), 4) == 1
     assert fast.decode_splits(ctx(16), 4) == 4 and fast.decode_splits(ctx(1), 1) == 64
+
+
+def test_which_gate_up_form_takes_a_small_step():
+    """the decode form up to 16 rows and while the activations are a tensor of less than 128 KB, the prompt form after"""
+    import torch
+    form = lambda m, width, stride=None: fast._swiglu_in_decode_form(      # noqa: E731
+        torch.empty((m, stride or width), dtype=torch.bfloat16)[:, :width])
+    assert [form(m, 2560) for m in (1, 16, 17, 25, 26, 32, 33, 128, 129)] == [True, True, True, True, False, False, False,
+                                                                              False, False]
+    assert form(63, 1024) and not form(64, 1024)               # a narrower model: 2 KB a row
+    assert not form(17, 5120) and form(12, 5120)               # a wider one
+    assert not form(17, 2560, stride=16384)                    # rows that lie far apart: the extent counts, not the bytes read
+    assert not form(200, 64)                                   # never beyond 128 rows

@@ -442,10 +442,13 @@ def test_decode_gate_up_product_finishes_swiglu_itself(K, M, F, K_):
         assert int(st.item()) == 0
         assert _rel(out.float(), ref) < 6e-3
         assert int(flags.abs().sum().item()) == 0
-    if M <= 32:
-        out = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
-        assert fast.gemm_swiglu_decode(a, wgu, out, st)          # the engine's way in, with scratch of its own
-        assert int(st.item()) == 0 and _rel(out.float(), ref) < 6e-3
+    # the engine's way in: the decode form (with scratch of its own) or the prompt form, whichever takes the shape
+    out = torch.full((M, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+    took = [fast.gemm_swiglu_decode(a, wgu, out, st), False]
+    if not took[0]:
+        took[1] = fast.gemm_swiglu_rows(a, wgu, out, st)
+    assert took == [fast._swiglu_in_decode_form(a), not fast._swiglu_in_decode_form(a)]
+    assert int(st.item()) == 0 and _rel(out.float(), ref) < 6e-3
 
 
 # ------------------------------------------------------------------------------------------------ small kernels
