@@ -112,3 +112,52 @@ def test_random_configuration_and_schedule(tmp_path, case):
     eng.cache.check()
     assert eng.cache.slots.n_held == 0 and all(g.pages.pool.n_held == 0 for g in eng.cache.groups), what
     assert worst <= TOL[dtype], "%s: differs from the plain model by %.3g" % (what, worst)
+
+
+@pytest.mark.parametrize("case", list(range(10)))
+def test_steps_that_mix_prompts_portions_and_single_tokens(tmp_path, case):
+    """the step function's general use: in one step every live sequence brings its own number of tokens (a whole
+    prompt, a portion that continues an earlier one, a single token), some sit the step out, new sequences join, and
+    any subset of rows is wanted; each wanted row against the plain model's row of the whole sequence"""
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.engine.engine import Engine
+    from kindi_b200.weights.random_init import write_random_model
+    rng = random.Random(5000 + case)
+    cfg = _draw_config(rng, False, odd=rng.random() < 0.3)
+    dtype = rng.choice(["float32", "bfloat16"])
+    folder = write_random_model(str(tmp_path / "m"), cfg, case, dtype=dtype)
+    model = P.load_model(folder)
+    reqs = tiny.random_requests(cfg["vocab_size"], [rng.choice([3, 17, 64, 65, 130, 200, 300])
+                                                    for _ in range(rng.randint(2, 10))], seed=case)
+    want = {rid: P.forward(model, toks).numpy() for rid, toks in reqs.items()}
+    max_batch = rng.randint(2, 6)
+    eng = Engine(folder, ctx=max_batch * 320 + 64, dtype=dtype, max_batch=max_batch,
+                 max_step_tokens=rng.choice([64, 128, 8192]), prompt_graph_tokens=rng.choice([0, 128, 512]))
+    waiting, live, worst = list(reqs), {}, 0.0                   # live: id -> [slot, tokens done]
+    while waiting or live:
+        while waiting and len(live) < max_batch and rng.random() < 0.7:
+            live[waiting.pop(0)] = [eng.alloc(), 0]
+        entries, who = [], []
+        for rid, (slot, done) in live.items():
+            if rng.random() < 0.2:
+                continue
+            k = min(len(reqs[rid]) - done, rng.choice([1, 1, 1, 2, 5, 33, 64, 100]))
+            wanted = tuple(sorted(rng.sample(range(k), rng.randint(0, k)))) if rng.random() < 0.5 else tuple(range(k))
+            entries.append(StepEntry(slot, tuple(reqs[rid][done:done + k]), wanted))
+            who.append((rid, done, wanted, k))
+        if not entries:
+            continue
+        out = eng.step(entries)
+        eng.check_status()
+        rows = out.cpu().numpy() if out is not None else None
+        at = 0
+        for rid, done, wanted, k in who:
+            for w in wanted:
+                worst = max(worst, float(np.abs(rows[at] - want[rid][done + w]).max() / np.abs(want[rid]).max()))
+                at += 1
+            live[rid][1] = done + k
+            if live[rid][1] == len(reqs[rid]):
+                eng.free(live.pop(rid)[0])
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and all(g.pages.pool.n_held == 0 for g in eng.cache.groups)
+    assert worst <= TOL[dtype], "case %d (%s, %r): differs from the plain model by %.3g" % (case, dtype, cfg, worst)
