@@ -97,7 +97,7 @@ __device__ __forceinline__ void at_ld_sum(const float* const (&p)[NS], const boo
 }
 template <int HD, bool DEC, bool ROPE = false>
 __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constant__ CUtensorMap kvmap,
-        const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
+        const bf16* KB_STEP_DATA q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
         float* __restrict__ part_ml, const int* __restrict__ slot, const int* __restrict__ q_start,
         const int* __restrict__ kv_len, int nh, int nkv, int G, float scale_log2e, int window,
         const int* __restrict__ table, int table_stride, int n_pages, int* status, AtRopeIn rp) {
@@ -480,7 +480,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
 
 // merge the position splits of a decode step in split order: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s
 // (kindi/nbq.cu:635-649)
-__global__ void k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
+__global__ void k_attn_merge(const float* KB_STEP_DATA part_o, const float* KB_STEP_DATA part_ml, int n_splits,
                              bf16* __restrict__ out, int ldo, const int* __restrict__ q_start, int nh, int HD) {
     // blockDim = 4 * HD: group g = threadIdx.x / HD adds the splits 16 g .. 16 g + 15 for its column, then the four
     // group sums are added in group order: every sum has a fixed order

@@ -85,7 +85,7 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
 
 template <int FT_HD>
 __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
-        const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
+        const bf16* KB_STEP_DATA q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
         const int* __restrict__ table, int table_stride, int n_pages, int* status) {
     constexpr int FT_TILE_BYTES = 64 * FT_HD * 2, FT_STAGE_BYTES = 2 * FT_TILE_BYTES, FT_Q_BYTES = 128 * FT_HD * 2;

@@ -76,6 +76,13 @@ __device__ __forceinline__ void kb_pdl_launch() {
     if (gridDim.x * gridDim.y * gridDim.z <= 1024u) kb_pdl_launch_now();
 }
 __device__ __forceinline__ void kb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A kernel parameter that points at what an earlier kernel of the same step wrote (activations, split-K planes,
+// partial results, logits) is marked KB_STEP_DATA and is NOT declared __restrict__: for a const __restrict__ pointer the
+// compiler may take the data for read-only during the whole kernel and move its loads above the wait (seen with the
+// 32-bit product: loads placed right after the wait were issued before it and read what the kernel before had not
+// written yet). Weights, tables and the step's metadata are written before the step's first kernel and keep
+// __restrict__: they are meant to be read early.
+#define KB_STEP_DATA
 
 extern int g_kb_pdl;            // 1: launches carry the programmatic-serialization attribute
 

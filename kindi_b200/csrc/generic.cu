@@ -50,7 +50,7 @@ extern "C" int kb_embed(const void* table, int wdtype, const int* tok, float* x,
 
 // ------------------------------------------------------------------------------------------------ logits: scale, soft cap
 // z = z * scale, then (cap > 0) z = cap * tanh(z / cap), in place: the options a head part may carry
-__global__ void k_logit_post(float* __restrict__ z, long long n, float scale, float cap) {
+__global__ void k_logit_post(float* KB_STEP_DATA z, long long n, float scale, float cap) {
     kb_pdl_launch();
     kb_pdl_wait();
     const float inv = cap > 0.0f ? 1.0f / cap : 0.0f;
@@ -108,7 +108,7 @@ __device__ __forceinline__ float4 kb_sum_planes4(float4 v, const float* __restri
 // pass for widths up to 4096) with all its loads in flight at once. Each element's own sum (residual, then the
 // planes in order) is the same in both forms.
 template <typename TY, typename TW, bool VEC>
-__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict__ x, const float* __restrict__ delta,
+__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, TY* __restrict__ y,
         const int* __restrict__ rows, int T, int E, int write_back, int* status) {
     extern __shared__ float sv[];
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* __restrict_
 // taken in another order than in k_add_rmsnorm, so the true 32-bit path, whose results must not depend on how many rows
 // a step has, never uses it.
 template <typename TW>
-__global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* __restrict__ x, const float* __restrict__ delta,
+__global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
     kb_pdl_launch();
     kb_pdl_wait();
@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* __restrict__ x,
 // One warp per row with the whole row in registers (widths up to NCH * 128): every load of the row and of the planes is
 // in flight before the first sum, and the row is read once. Same sums in the same order as k_add_rmsnorm_warp.
 template <typename TW, int NCH>
-__global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* __restrict__ x, const float* __restrict__ delta,
+__global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
     kb_pdl_launch();
     kb_pdl_wait();
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* __restrict__
 // behind other rows (a row of 2560 with six planes: 18 trips for one warp, 4 here). The planes are added in order;
 // the four warps' sums of squares are added in warp order.
 template <typename TW, int NC>
-__global__ void __launch_bounds__(256, 2) k_add_rmsnorm_row4(float* __restrict__ x, const float* __restrict__ delta,
+__global__ void __launch_bounds__(256, 2) k_add_rmsnorm_row4(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
     constexpr int PB = 12 / NC > 0 ? 12 / NC : 1;          // planes in flight
     __shared__ float s_ss[8];
@@ -474,9 +474,9 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
 // multiply-adds, so an output does not depend on the tile it lands in or on how many rows there are.
 #define GS_BM 64
 #define GS_BN 64
-#define GS_BK 16
+#define GS_BK 32
 template <typename TA, typename TW, typename TC>
-__global__ void __launch_bounds__(256) k_gemm_simt(const TA* __restrict__ A, const TW* __restrict__ W,
+__global__ void __launch_bounds__(256) k_gemm_simt(const TA* KB_STEP_DATA A, const TW* __restrict__ W,
         TC* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
     __shared__ float As[GS_BK][GS_BM + 1];
     __shared__ float Ws[GS_BK][GS_BN + 1];
@@ -489,15 +489,29 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const TA* __restrict__ A, con
     for (int i = 0; i < 4; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    // the next K block's elements are requested before this one is multiplied: their way from memory runs beside the
+    // products (the order of every output's sum does not change)
+    constexpr int PER = GS_BM * GS_BK / 256;
+    float ra[PER], rw[PER];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int e = tid + 256 * j, r = e / GS_BK, c = e % GS_BK;
+            const int m = m0 + r, n = n0 + r, k = k0 + c;
+            ra[j] = (m < M && k < K) ? kb_to_f<TA>(A[(size_t)m * lda + k]) : 0.0f;
+            rw[j] = (n < N && k < K) ? kb_to_f<TW>(W[(size_t)n * ldw + k]) : 0.0f;
+        }
+    };
+    fetch(0);
     for (int k0 = 0; k0 < K; k0 += GS_BK) {
-        for (int e = tid; e < GS_BM * GS_BK; e += 256) {
-            int r = e / GS_BK, c = e % GS_BK;
-            int m = m0 + r, k = k0 + c;
-            As[c][r] = (m < M && k < K) ? kb_to_f<TA>(A[(size_t)m * lda + k]) : 0.0f;
-            int n = n0 + r;
-            Ws[c][r] = (n < N && k < K) ? kb_to_f<TW>(W[(size_t)n * ldw + k]) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int e = tid + 256 * j, r = e / GS_BK, c = e % GS_BK;
+            As[c][r] = ra[j];
+            Ws[c][r] = rw[j];
         }
         __syncthreads();
+        if (k0 + GS_BK < K) fetch(k0 + GS_BK);
 #pragma unroll
         for (int k = 0; k < GS_BK; k++) {
             float a[4], b[4];
@@ -552,7 +566,7 @@ extern "C" int kb_gemm_simt(const void* A, int adtype, const void* W, int wdtype
 // angle is (float)pos * inv_freq[i] in 32-bit, cosine and sine by the accurate library functions, and the four
 // products are rounded one by one (kindi/nbq.cu:127-130).
 template <typename TIN, typename T>
-__global__ void k_rope_store(const TIN* __restrict__ in, int n_planes, size_t plane_stride, int ld_in,
+__global__ void k_rope_store(const TIN* KB_STEP_DATA in, int n_planes, size_t plane_stride, int ld_in,
         T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
         const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
         int hd, KbCacheView cv, int* status) {
@@ -631,7 +645,7 @@ __device__ __forceinline__ void kb_st2(float* p, float2 v) { *(float2*)p = v; }
 __device__ __forceinline__ void kb_st2(bf16* p, float2 v) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(v.x, v.y); }
 
 template <typename TIN, typename T>
-__global__ void __launch_bounds__(256) k_rope_store_row(const TIN* __restrict__ in, int n_planes, size_t plane_stride,
+__global__ void __launch_bounds__(256) k_rope_store_row(const TIN* KB_STEP_DATA in, int n_planes, size_t plane_stride,
         int ld_in, T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
         const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
         int hd, KbCacheView cv, int* status) {
@@ -753,10 +767,10 @@ __device__ __forceinline__ void kb_st8(bf16* p, const float* v) {
 // expressions, so the same bits) and are read from there, 64 bytes per item beside the item's own loads; without it
 // each block computes its row's and shares them through shared memory.
 template <typename TIN, typename T, bool PLANES, bool TABLE = false>
-__global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const TIN* __restrict__ in, int n_planes,
+__global__ void __launch_bounds__(256, PLANES ? 1 : 5) k_rope_store_row8(const TIN* KB_STEP_DATA in, int n_planes,
         size_t plane_stride, int ld_in, T* __restrict__ qout, int ldq, const float* __restrict__ inv_freq, int rot,
         const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv,
-        int hd, KbCacheView cv, int* status, const float2* __restrict__ cs_table) {
+        int hd, KbCacheView cv, int* status, const float2* KB_STEP_DATA cs_table) {
     extern __shared__ float2 cs[];                  // [rot / 2]: (cos, sin) of the row's angles
     kb_pdl_launch();
     kb_pdl_wait();
@@ -958,7 +972,7 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
 // of every sum depends on positions only: the same row gives the same bits whether it came in a prompt or alone.
 #define AG_MAX_HD 256
 template <typename T>
-__global__ void __launch_bounds__(128) k_attn_generic(const T* __restrict__ q, int ldq, T* __restrict__ out,
+__global__ void __launch_bounds__(128) k_attn_generic(const T* KB_STEP_DATA q, int ldq, T* __restrict__ out,
         int ldo, const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int Tn,
         int nh, int group, int hd, float scale, int window, KbCacheView cv, int* status) {
     __shared__ float qs[4][AG_MAX_HD];
@@ -1048,7 +1062,7 @@ extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int
 // ------------------------------------------------------------------------------------------------ SwiGLU
 // gu: [T][2F] = gate then up; out[t][i] = gate / (1 + exp(-gate)) * up (kindi/nbq.cu:461-467)
 template <typename TIN, typename T>
-__global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_stride, T* __restrict__ out, int F,
+__global__ void k_swiglu(const TIN* KB_STEP_DATA gu, int n_planes, size_t plane_stride, T* __restrict__ out, int F,
                          long long total, int group) {
     kb_pdl_launch();
     kb_pdl_wait();
@@ -1078,7 +1092,7 @@ __global__ void k_swiglu(const TIN* __restrict__ gu, int n_planes, size_t plane_
 
 // the same with a row per blockIdx.y and two neighbouring columns per thread (F even, aligned rows)
 template <typename TIN, typename T>
-__global__ void __launch_bounds__(256) k_swiglu2(const TIN* __restrict__ gu, int n_planes, size_t plane_stride,
+__global__ void __launch_bounds__(256) k_swiglu2(const TIN* KB_STEP_DATA gu, int n_planes, size_t plane_stride,
                                                   T* __restrict__ out, int F, int group) {
     kb_pdl_launch();
     kb_pdl_wait();
@@ -1109,7 +1123,7 @@ __global__ void __launch_bounds__(256) k_swiglu2(const TIN* __restrict__ gu, int
 
 // bf16 rows in, bf16 out, eight columns per thread with 16-byte accesses; exp and the division by the fast
 // intrinsics (their error is far below one bf16 rounding)
-__global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* __restrict__ gu, bf16* __restrict__ out, int F,
+__global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* KB_STEP_DATA gu, bf16* __restrict__ out, int F,
                                                       int group) {
     kb_pdl_launch();
     kb_pdl_wait();

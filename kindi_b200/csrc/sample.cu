@@ -100,7 +100,7 @@ __device__ unsigned long long sm_block_sum(unsigned long long v, unsigned long l
     return t;
 }
 
-__global__ void __launch_bounds__(SM_THREADS) k_sample(const float* __restrict__ logits, long long ld, int V,
+__global__ void __launch_bounds__(SM_THREADS) k_sample(const float* KB_STEP_DATA logits, long long ld, int V,
         float temperature, int top_k, float top_p, float min_p, int hf_order, const float* __restrict__ uniform,
         int* __restrict__ out) {
     __shared__ float s_v[32];
@@ -248,7 +248,7 @@ extern "C" int kb_sample(const float* logits, long long ld, int R, int V, float 
 
 // the repeat penalty: z[t] /= rp when positive, *= rp when negative, for each listed token of the row
 // (kindi/sampling.py:117-123). recent: [R][n_recent], each row's distinct recent tokens, padded with -1.
-__global__ void k_penalize(float* __restrict__ logits, long long ld, int V, const int* __restrict__ recent,
+__global__ void k_penalize(float* KB_STEP_DATA logits, long long ld, int V, const int* __restrict__ recent,
                            int n_recent, float rp) {
     kb_pdl_launch();
     kb_pdl_wait();
