@@ -95,7 +95,7 @@ __device__ __forceinline__ void gp_umma_commit(uint32_t bar) {
 template <int BN, int STAGES, typename TC>
 __global__ void __launch_bounds__(GP_THREADS) k_gemm_pair(const __grid_constant__ CUtensorMap mapA,
         const __grid_constant__ CUtensorMap mapW, TC* __restrict__ C, int M, int N, int K, int ldc, int* status,
-        int swiglu_ld, float* __restrict__ part, int* __restrict__ flags) {
+        int swiglu_ld, float* part, int* flags) {      // (shared with other CTAs of this launch: no __restrict__)
     using S = GpSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);

@@ -342,7 +342,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS) k_gemm_sk_swiglu(const __grid_constant__ CUtensorMap mapP,
         const __grid_constant__ CUtensorMap mapQ, bf16* __restrict__ H, int rowsP, int M, int K, int F, int ldh,
-        float* __restrict__ part, int* __restrict__ flags, int* status) {
+        float* part, int* flags, int* status) {      // (shared with other CTAs of this launch: no __restrict__)
     using S = TcSmem<BN, STAGES, 1, true>;
     extern __shared__ uint8_t smem_raw[];
     kb_pdl_launch_now();
