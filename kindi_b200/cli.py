@@ -196,5 +196,14 @@ def main(argv=None):
     if not a.cmd:
         p.print_help()
         return 1
-    return {"generate": cmd_generate, "verify": cmd_verify, "bench": cmd_bench, "info": cmd_info,
-            "random": cmd_random}[a.cmd](a)
+    try:
+        return {"generate": cmd_generate, "verify": cmd_verify, "bench": cmd_bench, "info": cmd_info,
+                "random": cmd_random}[a.cmd](a)
+    except BrokenPipeError:
+        # whoever read the output has gone (`... | head`): leave quietly, without Python's complaint at exit
+        import os
+        try:
+            os.dup2(os.open(os.devnull, os.O_WRONLY), sys.stdout.fileno())
+        except OSError:
+            pass
+        return 0
