@@ -62,7 +62,7 @@ class Sampler:
                 arr = np.full((R, n), -1, dtype=np.int32)
                 for i, r in enumerate(rec):
                     arr[i, :len(r)] = r
-                dev = torch.from_numpy(arr).to(logits.device)
+                dev = torch.from_numpy(arr).pin_memory().to(logits.device, non_blocking=True)
                 K._check(lib.kb_penalize(logits.data_ptr(), logits.stride(0), R, V, dev.data_ptr(), n,
                                          float(params.repeat_penalty), st), "penalize")
         if params.greedy:
@@ -70,7 +70,8 @@ class Sampler:
         else:
             if uniforms is None or len(uniforms) != R:
                 raise ValueError("temperature sampling needs one uniform number per row")
-            u = torch.tensor(list(uniforms), dtype=torch.float32).to(logits.device)
+            # (from pinned memory, without a wait: the host goes on to issue the next step meanwhile)
+            u = torch.tensor(list(uniforms), dtype=torch.float32).pin_memory().to(logits.device, non_blocking=True)
         K._check(lib.kb_sample(logits.data_ptr(), logits.stride(0), R, V, float(params.temperature),
                                int(params.top_k), float(params.top_p), float(params.min_p),
                                1 if params.order == "hf" else 0, None if u is None else u.data_ptr(),
