@@ -112,6 +112,24 @@ def test_sampling_kernel_against_the_plain_sampler(opts):
             assert got[r] == _plain_pick(z[r].astype(np.float64), us[r], params, hist[r]), (V, r, opts)
 
 
+@pytest.mark.parametrize("R", [19, 21, 38, 75, 160])
+def test_sampling_kernel_with_many_rows(R):
+    """a row is shared by eight, four, two CTAs or has one to itself, depending on how many rows there are: the same
+    picks as the plain sampler in every case, with ties and with a vocabulary that no slice divides"""
+    from kindi_b200.config.runtime import SamplingParams
+    from kindi_b200.sampling.sampler import Sampler
+    rng = np.random.RandomState(R)
+    for V, opts in ((1001, dict(temperature=0.8, top_p=0.9, top_k=40)), (4099, dict(temperature=1.2, top_p=0.7, top_k=0)),
+                    (331, dict(temperature=0.6, top_p=1.0, top_k=5, min_p=0.1, order="hf"))):
+        params = SamplingParams(**opts)
+        z = np.round(rng.randn(R, V) * 10) / 4.0                    # multiples of 0.25: ties everywhere
+        z = z.astype(np.float32)
+        us = [float(u) for u in rng.rand(R)]
+        got = Sampler("cuda").pick(torch.from_numpy(z).cuda(), params, us, None).tolist()
+        want = [_plain_pick(z[r].astype(np.float64), us[r], params) for r in range(R)]
+        assert got == want, (R, V, opts)
+
+
 def test_sampling_kernel_takes_minus_zero_for_zero():
     """logits of -0 and +0 are one value: a cut that falls on a zero keeps both (rounded logits, so ties abound)"""
     from kindi_b200.config.runtime import SamplingParams
