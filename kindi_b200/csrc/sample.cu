@@ -516,12 +516,15 @@ extern "C" int kb_sample(const float* logits, long long ld, int R, int V, float 
 #define SM_GO(S)                                                                                                      \
     kb_launch(k_sample<S>, R * S, SM_THREADS, 0, st, logits, ld, V, temperature, top_k, top_p, min_p, hf_order, uniform, \
               out)
-    if (R * 8 <= sms + 12) SM_GO(8);
-    else if (R * 4 <= sms + 12) SM_GO(4);
-    else if (R * 2 <= sms + 12) SM_GO(2);
-    else SM_GO(1);
+    // (a cluster size this device or partition cannot place is answered with an error at the launch: the next
+    // smaller one is tried then)
+    cudaError_t e = cudaErrorUnknown;
+    if (R * 8 <= sms + 12) e = SM_GO(8);
+    if (e != cudaSuccess && R * 4 <= sms + 12) { cudaGetLastError(); e = SM_GO(4); }
+    if (e != cudaSuccess && R * 2 <= sms + 12) { cudaGetLastError(); e = SM_GO(2); }
+    if (e != cudaSuccess) { cudaGetLastError(); e = SM_GO(1); }
 #undef SM_GO
-    KB_LAUNCH_RET();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 // the repeat penalty: z[t] /= rp when positive, *= rp when negative, for each listed token of the row
