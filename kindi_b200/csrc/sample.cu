@@ -509,19 +509,23 @@ k_sample(const float* KB_STEP_DATA logits, long long ld, int V, float temperatur
 extern "C" int kb_sample(const float* logits, long long ld, int R, int V, float temperature, int top_k, float top_p,
                          float min_p, int hf_order, const float* uniform, int* out, cudaStream_t st) {
     if (R <= 0) return 0;
-    // as many CTAs a row as keep the whole launch within one wave of the SMs
+    // As many CTAs a row as keep the whole launch in one wave. A CTA of 1024 threads has an SM to itself, and a cluster
+    // has to fit into one GPC: measured on a B200 (148 SMs), 96 CTAs in clusters of eight and 128 in clusters of four
+    // or two run at once; one row more and the launch takes two rounds (top-k + top-p, 166,144 logits: 12 rows in
+    // eights 108 us, 16 rows 198 us in eights and 133 us in fours).
     int sms = 148, dev = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int room8 = sms * 2 / 3, room = sms - sms / 8;
 #define SM_GO(S)                                                                                                      \
     kb_launch(k_sample<S>, R * S, SM_THREADS, 0, st, logits, ld, V, temperature, top_k, top_p, min_p, hf_order, uniform, \
               out)
     // (a cluster size this device or partition cannot place is answered with an error at the launch: the next
     // smaller one is tried then)
     cudaError_t e = cudaErrorUnknown;
-    if (R * 8 <= sms + 12) e = SM_GO(8);
-    if (e != cudaSuccess && R * 4 <= sms + 12) { cudaGetLastError(); e = SM_GO(4); }
-    if (e != cudaSuccess && R * 2 <= sms + 12) { cudaGetLastError(); e = SM_GO(2); }
+    if (R * 8 <= room8) e = SM_GO(8);
+    if (e != cudaSuccess && R * 4 <= room) { cudaGetLastError(); e = SM_GO(4); }
+    if (e != cudaSuccess && R * 2 <= room) { cudaGetLastError(); e = SM_GO(2); }
     if (e != cudaSuccess) { cudaGetLastError(); e = SM_GO(1); }
 #undef SM_GO
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
