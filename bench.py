@@ -222,7 +222,7 @@ def bench_decode(eng, batch: int, context: int, steps: int, warmup: int, e2e: bo
     return dev_ms, e2e_ms, launches, bytes_step
 
 
-def bench_e2e(eng, batch: int, context: int, steps: int, warm: int = 48) -> float:
+def bench_e2e(eng, batch: int, context: int, steps: int, warm: int = 48, sampling=None) -> float:
     """milliseconds per decode step through the call a user makes, ``Engine.generate_batch``: `batch` prompts of
     context - 1 token ids given as Python lists, greedy tokens returned as Python lists. Every step copies its inputs
     (positions, lengths, slots, row lists, tokens) from pinned host memory to the device and reads its picked tokens
@@ -234,11 +234,12 @@ def bench_e2e(eng, batch: int, context: int, steps: int, warm: int = 48) -> floa
     rng = random.Random(5)
     vocab = eng.spec.vocab_size
     prompts = [[rng.randrange(vocab) for _ in range(context - 1)] for _ in range(batch)]
-    eng.generate_batch([p[:64] for p in prompts], temperature=0.0, max_tokens=8, stop_token_ids=())       # warm-up
+    how = dict(sampling) if sampling else dict(temperature=0.0)       # greedy, unless sampling options are given
+    eng.generate_batch([p[:64] for p in prompts], max_tokens=8, stop_token_ids=(), **how)       # warm-up
     torch.cuda.synchronize()
     stamps = []
-    res = eng.generate_batch(prompts, temperature=0.0, max_tokens=warm + steps + 1, stop_token_ids=(),
-                             on_tokens=lambda d: stamps.append(time.perf_counter()))
+    res = eng.generate_batch(prompts, max_tokens=warm + steps + 1, stop_token_ids=(),
+                             on_tokens=lambda d: stamps.append(time.perf_counter()), **how)
     assert all(len(t) == warm + steps + 1 for t in res.tokens) and len(stamps) == warm + steps + 1
     return (stamps[-1] - stamps[-1 - steps]) * 1000.0 / steps
 
@@ -469,6 +470,9 @@ def main(argv=None) -> int:
                          "Python entry point (the 16B-class configuration's workload)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement (for profiling runs)")
+    ap.add_argument("--sampled", action="store_true",
+                    help="also measure the end-to-end decode step with the reference's default sampling (temperature "
+                         "0.7, top-p 0.8, top-k 20) and report it as e2e_sampled")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill (for profiling)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
@@ -547,6 +551,10 @@ def main(argv=None) -> int:
                      "unit": "GB/s", "frac": round(bytes_step / dev_ms / 1e6 / pk["hbm_gbs"], 4),
                      "of": pk["source"], "bytes_per_step": int(bytes_step)},
     }
+    if a.sampled:
+        sms = bench_e2e(eng, a.batch, a.context, a.steps, sampling=dict(temperature=0.7, top_p=0.8, top_k=20, seed=1))
+        out["e2e_sampled"] = {"value": round(a.batch * 1000.0 / sms, 1), "unit": "tokens/s", "ms_per_step": round(sms, 4),
+                              "sampling": "temperature 0.7, top-p 0.8, top-k 20"}
     if not a.no_points:
         T = PREFILL_TOKENS
         # (the median of 20 passes back to back: under that sustained load the GPU runs slower than in a burst, which
